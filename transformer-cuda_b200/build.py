@@ -1,0 +1,71 @@
+"""Builds the engine in-tree with nvcc for sm_100a: lib/libb200attn.so (C ABI + the C++ launch API)
+and lib/libb200attn.a (the same objects, for static linking in place of the reference's
+src/kernels/attention.cu). Rebuilds only when a source is newer than the library."""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+OBJDIR = os.path.join(LIBDIR, "obj")
+SOURCES = ["api.cu", "launch_api.cu", "layout_kernels.cu", "softmax_kernels.cu", "attn_f32.cu", "attn_tc_fwd.cu",
+           "attn_tc_bwd.cu"]
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
+SO = os.path.join(LIBDIR, "libb200attn.so")
+AR = os.path.join(LIBDIR, "libb200attn.a")
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found: the engine has no prebuilt or CPU fallback")
+
+
+def _stale(target, deps):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(verbose=False, force=False, ptxas_info=False):
+    os.makedirs(OBJDIR, exist_ok=True)
+    nvcc = _nvcc()
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers += [os.path.join(HERE, "..", "include", "b200attn.h"),
+                os.path.join(HERE, "..", "include", "kernels", "attention.cuh")]
+    objs, procs = [], []
+    for src in SOURCES:
+        s = os.path.join(CSRC, src)
+        o = os.path.join(OBJDIR, src.replace(".cu", ".o"))
+        objs.append(o)
+        if force or _stale(o, [s] + headers):
+            cmd = [nvcc] + ARCH + FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", s, "-o", o]
+            if verbose:
+                print(" ".join(cmd), flush=True)
+            procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    failed = False
+    for src, p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0:
+            failed = True
+            sys.stderr.write(f"--- nvcc failed for {src} ---\n{out}\n")
+        elif verbose or ptxas_info:
+            print(out)
+    if failed:
+        raise RuntimeError("nvcc compilation failed")
+    if force or _stale(SO, objs):
+        subprocess.check_call([nvcc] + ARCH + ["-shared", "-o", SO] + objs + ["-lcudart"])
+    if force or _stale(AR, objs):
+        if os.path.exists(AR):
+            os.remove(AR)
+        subprocess.check_call(["ar", "rcs", AR] + objs)
+    return SO
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv))

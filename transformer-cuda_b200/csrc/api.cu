@@ -1,0 +1,539 @@
+// Host side of the engine: the extern "C" entry points declared in include/b200attn.h.
+// Validates arguments, owns the per-device scratch memory and the device fault word, builds the
+// TMA tensor maps, and dispatches to the kernels. No entry point synchronises or allocates on the
+// hot path once scratch has been reserved; nothing here has a CPU fallback.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200attn.h"
+#include "kernels.cuh"
+
+namespace {
+
+using namespace b200attn;
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+int fail_cuda(cudaError_t e, const char* what) {
+    return fail(B200ATTN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define RETURN_IF_CUDA(expr, what)                      \
+    do {                                                \
+        cudaError_t _e = (expr);                        \
+        if (_e != cudaSuccess) return fail_cuda(_e, what); \
+    } while (0)
+
+int initial_math_mode() {
+    const char* s = getenv("B200ATTN_MATH");
+    if (s && (strcmp(s, "bf16") == 0 || strcmp(s, "BF16") == 0 || strcmp(s, "1") == 0)) return B200ATTN_MATH_BF16;
+    return B200ATTN_MATH_FP32;
+}
+std::atomic<int> g_math_mode{initial_math_mode()};
+
+// ------------------------------------------------------------------ per-device state
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    bool ready = false;
+    bool is_sm100 = false;
+    unsigned int* fault_word = nullptr;  // device memory, 4 bytes
+    uint8_t* scratch = nullptr;
+    size_t scratch_bytes = 0;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mutex;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+bool stream_is_capturing(cudaStream_t s) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return st != cudaStreamCaptureStatusNone;
+}
+
+// Looks up (and on first use initialises) the state of the current device.
+int device_state(cudaStream_t stream, DeviceState** out) {
+    int dev = 0;
+    RETURN_IF_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(B200ATTN_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        if (stream_is_capturing(stream))
+            return fail(B200ATTN_ERR_SCRATCH, "first use on device %d happens inside a stream capture; call b200attn_reserve before capturing", dev);
+        int major = 0, minor = 0;
+        RETURN_IF_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev), "cudaDeviceGetAttribute");
+        RETURN_IF_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev), "cudaDeviceGetAttribute");
+        st.is_sm100 = (major == 10);
+        RETURN_IF_CUDA(cudaMalloc(&st.fault_word, sizeof(unsigned int)), "cudaMalloc(fault word)");
+        RETURN_IF_CUDA(cudaMemset(st.fault_word, 0, sizeof(unsigned int)), "cudaMemset(fault word)");
+        if (!g_encode) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            RETURN_IF_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q),
+                           "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+            if (!fn) return fail(B200ATTN_ERR_CUDA, "driver does not export cuTensorMapEncodeTiled");
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        st.ready = true;
+    }
+    *out = &st;
+    return B200ATTN_OK;
+}
+
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Makes the scratch of this device at least `bytes` large. Growing synchronises the device and
+// is refused while `stream` is capturing.
+int ensure_scratch(DeviceState* st, size_t bytes, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (st->scratch_bytes >= bytes) return B200ATTN_OK;
+    if (stream_is_capturing(stream))
+        return fail(B200ATTN_ERR_SCRATCH, "scratch of %zu bytes needed but only %zu reserved, and the stream is capturing; call b200attn_reserve first",
+                    bytes, st->scratch_bytes);
+    RETURN_IF_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize before growing scratch");
+    if (st->scratch) RETURN_IF_CUDA(cudaFree(st->scratch), "cudaFree(scratch)");
+    st->scratch = nullptr;
+    st->scratch_bytes = 0;
+    size_t want = round_up(bytes, size_t(1) << 20);
+    RETURN_IF_CUDA(cudaMalloc(&st->scratch, want), "cudaMalloc(scratch)");
+    st->scratch_bytes = want;
+    return B200ATTN_OK;
+}
+
+// Scratch demand of the largest consumer (b200attn_bwd_f32 in BF16 mode and b200attn_bwd_bf16).
+size_t scratch_for(long long BH, long long T, long long d) {
+    const size_t n = size_t(BH) * T * d, rows = size_t(BH) * T;
+    size_t f32_api = 4 * round_up(n * 2, 256) + round_up(rows * 4, 256);        // bf16 q,k,v,dO + lse2
+    size_t bf16_api = round_up(n * 4, 256) + 2 * round_up(rows * 4, 256);       // dq accumulator + D + lse2
+    return (f32_api > bf16_api ? f32_api : bf16_api) + 256;
+}
+
+struct Bump {
+    uint8_t* p;
+    template <typename T>
+    T* take(size_t count) {
+        T* r = reinterpret_cast<T*>(p);
+        p += round_up(count * sizeof(T), 256);
+        return r;
+    }
+};
+
+// (d, T, BH) BF16 tensor viewed through 64 x 128 x 1 boxes with the 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* base, int BH, int T, int d) {
+    cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
+    cuuint64_t strides[2] = {cuuint64_t(d) * 2, cuuint64_t(T) * d * 2};
+    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (BH=%d T=%d d=%d)", int(r), BH, T, d);
+    return B200ATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_dims4(const char* fn, int B, int H, int T, int d) {
+    if (B < 0 || H < 0 || T < 0 || d <= 0) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: negative size or d <= 0 (B=%d H=%d T=%d d=%d)", fn, B, H, T, d);
+    if ((long long)B * H > 0x7fffffffLL) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: B*H too large", fn);
+    return B200ATTN_OK;
+}
+#define REQUIRE_PTR(fn, p) \
+    if ((p) == nullptr) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: argument '%s' is NULL", fn, #p)
+
+int tc_supported(const char* fn, DeviceState* st, int d) {
+    if (!st->is_sm100) return fail(B200ATTN_ERR_UNSUPPORTED, "%s: the tensor-core path needs an sm_100a device (B200)", fn);
+    if (d != 64 && d != 128) return fail(B200ATTN_ERR_UNSUPPORTED, "%s: the tensor-core path supports d in {64,128}, got %d", fn, d);
+    return B200ATTN_OK;
+}
+
+int run_fwd_tc(DeviceState* st, const void* q, const void* k, const void* v, void* out, bool out_f32, float* m_out,
+               float* l_out, float* lse_out, int BH, int T, int d, float scale, cudaStream_t stream) {
+    TcFwdArgs a;
+    memset(&a, 0, sizeof(a));
+    int rc;
+    if ((rc = make_map(&a.map_q, q, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_k, k, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_v, v, BH, T, d))) return rc;
+    if (!out_f32) {
+        if ((rc = make_map(&a.map_o, out, BH, T, d))) return rc;
+    }
+    a.out = out;
+    a.out_is_f32 = out_f32 ? 1 : 0;
+    a.m_out = m_out;
+    a.l_out = l_out;
+    a.lse_out = lse_out;
+    a.BH = BH, a.T = T, a.d = d;
+    a.scale = scale;
+    a.fault_word = st->fault_word;
+    RETURN_IF_CUDA(launch_attn_fwd_tc(a, stream), "tensor-core forward launch");
+    return B200ATTN_OK;
+}
+
+int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, const void* dO, const float* lse2,
+               const float* D, float* dq_acc, void* dk, void* dv, bool grads_f32, int BH, int T, int d, float scale,
+               cudaStream_t stream) {
+    TcBwdArgs a;
+    memset(&a, 0, sizeof(a));
+    int rc;
+    if ((rc = make_map(&a.map_q, q, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_k, k, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_v, v, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_do, dO, BH, T, d))) return rc;
+    if (!grads_f32) {
+        if ((rc = make_map(&a.map_dk, dk, BH, T, d))) return rc;
+        if ((rc = make_map(&a.map_dv, dv, BH, T, d))) return rc;
+    }
+    a.lse2 = lse2;
+    a.D = D;
+    a.dq_acc = dq_acc;
+    a.dk = dk;
+    a.dv = dv;
+    a.grads_are_f32 = grads_f32 ? 1 : 0;
+    a.BH = BH, a.T = T, a.d = d;
+    a.scale = scale;
+    a.fault_word = st->fault_word;
+    RETURN_IF_CUDA(launch_attn_bwd_tc(a, stream), "tensor-core backward launch");
+    return B200ATTN_OK;
+}
+
+}  // namespace
+
+// ====================================================================== library state
+extern "C" int b200attn_version(void) { return 100; }
+
+extern "C" const char* b200attn_last_error(void) { return g_error; }
+
+extern "C" int b200attn_set_math_mode(int mode) {
+    if (mode != B200ATTN_MATH_FP32 && mode != B200ATTN_MATH_BF16)
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "b200attn_set_math_mode: unknown mode %d", mode);
+    g_math_mode.store(mode);
+    return B200ATTN_OK;
+}
+extern "C" int b200attn_get_math_mode(void) { return g_math_mode.load(); }
+
+extern "C" int b200attn_reserve(int BH, int T, int d) {
+    if (BH < 0 || T < 0 || d <= 0) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "b200attn_reserve: bad shape (BH=%d T=%d d=%d)", BH, T, d);
+    DeviceState* st = nullptr;
+    int rc = device_state(nullptr, &st);
+    if (rc) return rc;
+    return ensure_scratch(st, scratch_for(BH, T, d), nullptr);
+}
+
+extern "C" int b200attn_release(void) {
+    int dev = 0;
+    RETURN_IF_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) return B200ATTN_OK;
+    RETURN_IF_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    if (st.scratch) cudaFree(st.scratch);
+    st.scratch = nullptr;
+    st.scratch_bytes = 0;
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_check_device_fault(unsigned int* code) {
+    DeviceState* st = nullptr;
+    int rc = device_state(nullptr, &st);
+    if (rc) return rc;
+    RETURN_IF_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    unsigned int w = 0;
+    RETURN_IF_CUDA(cudaMemcpy(&w, st->fault_word, sizeof(w), cudaMemcpyDeviceToHost), "cudaMemcpy(fault word)");
+    if (code) *code = w;
+    if (w != 0) {
+        RETURN_IF_CUDA(cudaMemset(st->fault_word, 0, sizeof(w)), "cudaMemset(fault word)");
+        return fail(B200ATTN_ERR_DEVICE_FAULT, "a bounded wait inside a kernel ran out (fault word 0x%08x)", w);
+    }
+    return B200ATTN_OK;
+}
+
+// ====================================================================== FP32 API
+extern "C" int b200attn_qkv_split_f32(const float* qkv, float* q, float* k, float* v, int B, int T, int H, int d,
+                                      b200attn_stream_t stream) {
+    const char* fn = "b200attn_qkv_split_f32";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, qkv); REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v);
+    RETURN_IF_CUDA(launch_qkv_split<float>(qkv, q, k, v, B, T, H, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_qkv_merge_grad_f32(const float* dq, const float* dk, const float* dv, float* dqkv, int B,
+                                           int T, int H, int d, b200attn_stream_t stream) {
+    const char* fn = "b200attn_qkv_merge_grad_f32";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dq); REQUIRE_PTR(fn, dk); REQUIRE_PTR(fn, dv); REQUIRE_PTR(fn, dqkv);
+    RETURN_IF_CUDA(launch_qkv_merge_grad<float>(dq, dk, dv, dqkv, B, T, H, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_causal_softmax_fwd_f32(const float* scores, float* probs, int B, int H, int T, float scale,
+                                               b200attn_stream_t stream) {
+    const char* fn = "b200attn_causal_softmax_fwd_f32";
+    int rc = check_dims4(fn, B, H, T, 1);
+    if (rc) return rc;
+    long long rows = (long long)B * H * T;
+    if (rows == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, scores); REQUIRE_PTR(fn, probs);
+    RETURN_IF_CUDA(launch_causal_softmax_fwd(scores, probs, rows, T, scale, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_causal_softmax_bwd_f32(const float* dprobs, const float* probs, float* dscores, int B, int H,
+                                               int T, float scale, b200attn_stream_t stream) {
+    const char* fn = "b200attn_causal_softmax_bwd_f32";
+    int rc = check_dims4(fn, B, H, T, 1);
+    if (rc) return rc;
+    long long rows = (long long)B * H * T;
+    if (rows == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dprobs); REQUIRE_PTR(fn, probs); REQUIRE_PTR(fn, dscores);
+    RETURN_IF_CUDA(launch_causal_softmax_bwd(dprobs, probs, dscores, rows, T, scale, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_fwd_f32(const float* q, const float* k, const float* v, float* out, int B, int H, int T, int d,
+                                float scale, float* m_out, float* l_out, b200attn_stream_t stream_) {
+    const char* fn = "b200attn_fwd_f32";
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    const int BH = B * H;
+    if ((long long)BH * T == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v); REQUIRE_PTR(fn, out);
+    if (g_math_mode.load() == B200ATTN_MATH_FP32) {
+        if (d > 256) return fail(B200ATTN_ERR_UNSUPPORTED, "%s: FP32 mode supports d <= 256, got %d", fn, d);
+        RETURN_IF_CUDA(launch_attn_fwd_f32(q, k, v, out, m_out, l_out, BH, T, d, scale, stream), fn);
+        return B200ATTN_OK;
+    }
+    // BF16 mode: round the operands to BF16 in scratch, run the tensor-core kernel, write FP32 results.
+    DeviceState* st = nullptr;
+    if ((rc = device_state(stream, &st))) return rc;
+    if ((rc = tc_supported(fn, st, d))) return rc;
+    if (!aligned16(out)) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: out must be 16-byte aligned", fn);
+    const size_t n = size_t(BH) * T * d;
+    if ((rc = ensure_scratch(st, scratch_for(BH, T, d), stream))) return rc;
+    Bump bump{st->scratch};
+    __nv_bfloat16* qb = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* kb = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* vb = bump.take<__nv_bfloat16>(n);
+    RETURN_IF_CUDA(launch_f32_to_bf16(q, qb, (long long)n, stream), "convert q");
+    RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
+    RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
+    return run_fwd_tc(st, qb, kb, vb, out, true, m_out, l_out, nullptr, BH, T, d, scale, stream);
+}
+
+extern "C" int b200attn_dot_do_o_f32(const float* dO, const float* O, float* D, int B, int H, int T, int d,
+                                     b200attn_stream_t stream) {
+    const char* fn = "b200attn_dot_do_o_f32";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    long long rows = (long long)B * H * T;
+    if (rows == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dO); REQUIRE_PTR(fn, O); REQUIRE_PTR(fn, D);
+    RETURN_IF_CUDA(launch_dot_do_o_f32(dO, O, D, rows, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_bwd_f32(const float* q, const float* k, const float* v, const float* o, const float* dO,
+                                const float* m, const float* l, float* dq, float* dk, float* dv, float* workspace,
+                                int B, int H, int T, int d, float scale, b200attn_stream_t stream_) {
+    const char* fn = "b200attn_bwd_f32";
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    const int BH = B * H;
+    const long long rows = (long long)BH * T;
+    if (rows == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v); REQUIRE_PTR(fn, o); REQUIRE_PTR(fn, dO);
+    REQUIRE_PTR(fn, m); REQUIRE_PTR(fn, l); REQUIRE_PTR(fn, dq); REQUIRE_PTR(fn, dk); REQUIRE_PTR(fn, dv);
+    REQUIRE_PTR(fn, workspace);
+    if (g_math_mode.load() == B200ATTN_MATH_FP32) {
+        if (d > 256) return fail(B200ATTN_ERR_UNSUPPORTED, "%s: FP32 mode supports d <= 256, got %d", fn, d);
+        RETURN_IF_CUDA(launch_dot_do_o_f32(dO, o, workspace, rows, d, stream), "D pre-pass");
+        RETURN_IF_CUDA(launch_attn_bwd_f32(q, k, v, dO, m, l, workspace, dq, dk, dv, BH, T, d, scale, stream), fn);
+        return B200ATTN_OK;
+    }
+    DeviceState* st = nullptr;
+    if ((rc = device_state(stream, &st))) return rc;
+    if ((rc = tc_supported(fn, st, d))) return rc;
+    if (!aligned16(dq) || !aligned16(dk) || !aligned16(dv) || !aligned16(o) || !aligned16(dO))
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", fn);
+    const size_t n = size_t(BH) * T * d;
+    if ((rc = ensure_scratch(st, scratch_for(BH, T, d), stream))) return rc;
+    Bump bump{st->scratch};
+    __nv_bfloat16* qb = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* kb = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* vb = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* dob = bump.take<__nv_bfloat16>(n);
+    float* lse2 = bump.take<float>(size_t(rows));
+    RETURN_IF_CUDA(launch_f32_to_bf16(q, qb, (long long)n, stream), "convert q");
+    RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
+    RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
+    RETURN_IF_CUDA(launch_f32_to_bf16(dO, dob, (long long)n, stream), "convert dO");
+    RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, rows, d, stream), "pre-pass");
+    // dq is the FP32 accumulator itself: partial sums are reduced straight into the caller's buffer
+    RETURN_IF_CUDA(cudaMemsetAsync(dq, 0, n * sizeof(float), stream), "cudaMemsetAsync(dq)");
+    return run_bwd_tc(st, qb, kb, vb, dob, lse2, workspace, dq, dk, dv, true, BH, T, d, scale, stream);
+}
+
+extern "C" int b200attn_merge_heads_f32(const float* in, float* out, int B, int H, int T, int d,
+                                        b200attn_stream_t stream) {
+    const char* fn = "b200attn_merge_heads_f32";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, in); REQUIRE_PTR(fn, out);
+    RETURN_IF_CUDA(launch_merge_heads<float>(in, out, B, H, T, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_split_heads_f32(const float* dout, float* din, int B, int H, int T, int d,
+                                        b200attn_stream_t stream) {
+    const char* fn = "b200attn_split_heads_f32";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dout); REQUIRE_PTR(fn, din);
+    RETURN_IF_CUDA(launch_split_heads<float>(dout, din, B, H, T, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+// ====================================================================== BF16 API
+extern "C" int b200attn_fwd_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int BH, int T,
+                                 int d, float scale, b200attn_stream_t stream_) {
+    const char* fn = "b200attn_fwd_bf16";
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_dims4(fn, BH, 1, T, d);
+    if (rc) return rc;
+    if ((long long)BH * T == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v); REQUIRE_PTR(fn, out); REQUIRE_PTR(fn, lse);
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", fn);
+    DeviceState* st = nullptr;
+    if ((rc = device_state(stream, &st))) return rc;
+    if ((rc = tc_supported(fn, st, d))) return rc;
+    return run_fwd_tc(st, q, k, v, out, false, nullptr, nullptr, lse, BH, T, d, scale, stream);
+}
+
+extern "C" int b200attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                                 const float* lse, void* dq, void* dk, void* dv, int BH, int T, int d, float scale,
+                                 b200attn_stream_t stream_) {
+    const char* fn = "b200attn_bwd_bf16";
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_dims4(fn, BH, 1, T, d);
+    if (rc) return rc;
+    const long long rows = (long long)BH * T;
+    if (rows == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v); REQUIRE_PTR(fn, o); REQUIRE_PTR(fn, dO);
+    REQUIRE_PTR(fn, lse); REQUIRE_PTR(fn, dq); REQUIRE_PTR(fn, dk); REQUIRE_PTR(fn, dv);
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv))
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", fn);
+    DeviceState* st = nullptr;
+    if ((rc = device_state(stream, &st))) return rc;
+    if ((rc = tc_supported(fn, st, d))) return rc;
+    const size_t n = size_t(BH) * T * d;
+    if ((rc = ensure_scratch(st, scratch_for(BH, T, d), stream))) return rc;
+    Bump bump{st->scratch};
+    float* dq_acc = bump.take<float>(n);
+    float* D = bump.take<float>(size_t(rows));
+    float* lse2 = bump.take<float>(size_t(rows));
+    const __nv_bfloat16* ob = static_cast<const __nv_bfloat16*>(o);
+    const __nv_bfloat16* dob = static_cast<const __nv_bfloat16*>(dO);
+    RETURN_IF_CUDA(launch_bwd_prepass<__nv_bfloat16>(ob, dob, nullptr, nullptr, lse, D, lse2, rows, d, stream), "pre-pass");
+    RETURN_IF_CUDA(cudaMemsetAsync(dq_acc, 0, n * sizeof(float), stream), "cudaMemsetAsync(dq accumulator)");
+    if ((rc = run_bwd_tc(st, q, k, v, dO, lse2, D, dq_acc, dk, dv, false, BH, T, d, scale, stream))) return rc;
+    RETURN_IF_CUDA(launch_dq_convert(dq_acc, static_cast<__nv_bfloat16*>(dq), (long long)n, stream), "dq convert");
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_qkv_split_bf16(const float* qkv, void* q, void* k, void* v, int B, int T, int H, int d,
+                                       b200attn_stream_t stream) {
+    const char* fn = "b200attn_qkv_split_bf16";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, qkv); REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v);
+    RETURN_IF_CUDA(launch_qkv_split<__nv_bfloat16>(qkv, static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k),
+                                                   static_cast<__nv_bfloat16*>(v), B, T, H, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_qkv_merge_grad_bf16(const void* dq, const void* dk, const void* dv, float* dqkv, int B, int T,
+                                            int H, int d, b200attn_stream_t stream) {
+    const char* fn = "b200attn_qkv_merge_grad_bf16";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dq); REQUIRE_PTR(fn, dk); REQUIRE_PTR(fn, dv); REQUIRE_PTR(fn, dqkv);
+    RETURN_IF_CUDA(launch_qkv_merge_grad<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(dq),
+                                                        static_cast<const __nv_bfloat16*>(dk),
+                                                        static_cast<const __nv_bfloat16*>(dv), dqkv, B, T, H, d,
+                                                        (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_merge_heads_bf16(const void* in, float* out, int B, int H, int T, int d,
+                                         b200attn_stream_t stream) {
+    const char* fn = "b200attn_merge_heads_bf16";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, in); REQUIRE_PTR(fn, out);
+    RETURN_IF_CUDA(launch_merge_heads<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(in), out, B, H, T, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_split_heads_bf16(const float* dout, void* din, int B, int H, int T, int d,
+                                         b200attn_stream_t stream) {
+    const char* fn = "b200attn_split_heads_bf16";
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * T * H == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dout); REQUIRE_PTR(fn, din);
+    RETURN_IF_CUDA(launch_split_heads<__nv_bfloat16>(dout, static_cast<__nv_bfloat16*>(din), B, H, T, d, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+// ====================================================================== synthetic inputs
+extern "C" int b200attn_fill_normal_f32(float* dst, long long n, unsigned long long seed, long long offset,
+                                        b200attn_stream_t stream) {
+    const char* fn = "b200attn_fill_normal_f32";
+    if (n < 0 || offset < 0) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: negative count or offset", fn);
+    if (n == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dst);
+    RETURN_IF_CUDA(launch_fill_normal_f32(dst, n, seed, offset, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_fill_normal_bf16(void* dst, long long n, unsigned long long seed, long long offset,
+                                         b200attn_stream_t stream) {
+    const char* fn = "b200attn_fill_normal_bf16";
+    if (n < 0 || offset < 0) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: negative count or offset", fn);
+    if (n == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, dst);
+    RETURN_IF_CUDA(launch_fill_normal_bf16(static_cast<__nv_bfloat16*>(dst), n, seed, offset, (cudaStream_t)stream), fn);
+    return B200ATTN_OK;
+}

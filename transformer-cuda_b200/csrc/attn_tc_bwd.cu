@@ -1,0 +1,461 @@
+// Causal attention backward on the sm_100a tensor cores (tcgen05): dQ, dK, dV from Q, K, V, dO,
+// the log-sum-exp of the forward pass and D = rowsum(dO*O). Computes what
+// tiled_causal_attention_backward of sarimahsan/transformer-cuda computes
+// (src/kernels/attention.cu:697-1011) with five GEMMs per (key tile, query tile) pair instead of the
+// reference's seven dot-product passes, and for head dims 64 and 128.
+//
+// One CTA owns one 128-row key/value tile j of one (batch, head) slab and walks the query tiles
+// i = j .. last (tiles before the diagonal are skipped). Scores are produced TRANSPOSED, so that
+// thread r of the compute warps owns key row r (TMEM lane r) and the columns are queries:
+//
+//   S^T  = K_j Q_i^T                  (SS MMA, both operands K-major)        -> TMEM
+//   dP^T = V_j dO_i^T                 (SS MMA)                               -> TMEM
+//   P^T  = exp2(S^T*scale*log2e - lse2[q])   written BF16 over S^T in TMEM
+//   dV  += P^T dO_i                   (TS MMA: A = P^T from TMEM, dO_i MN-major)
+//   dS^T = P^T * (dP^T - D[q]) * scale       written BF16 to shared memory, 128B-swizzled
+//   dK  += dS^T Q_i                   (SS MMA: A = dS^T K-major, Q_i MN-major)
+//   dQ_i = dS K_j                     (SS MMA: the same dS^T tile read as an MN-major A, K_j MN-major)
+//
+// dQ_i is a partial sum over key tiles: the compute warps read it from TMEM and add it to an FP32
+// accumulator in global memory with 16-byte vector reductions (red.global.add.v4.f32). dK and dV
+// stay in TMEM for the whole loop and are written once.
+//
+// Warps 0-3 compute, warp 4 is the TMA producer (no multicast), warp 5 issues the MMAs.
+// TMEM columns, D = 64:  S/P^T [0,128) dP^T [128,256) dV [256,320) dK [320,384) dQ [384,448)
+//               D = 128: S/P^T [0,128) dP^T and dQ share [128,256) dV [256,384) dK [384,512)
+// Every wait is bounded (tc_common.cuh).
+#include "kernels.cuh"
+#include "tc_common.cuh"
+
+namespace b200attn {
+namespace {
+
+constexpr int kBQ = 128;               // query rows per inner tile
+constexpr int kBKV = 128;              // key/value rows per CTA
+constexpr int kAtomBytes = 128 * 128;  // 128 rows x 64 bf16, 128-byte swizzled
+constexpr int kComputeThreads = 128;
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D>
+struct BwdCfg {
+    static constexpr int kAtoms = D / 64;
+    static constexpr int kTileBytes = kAtoms * kAtomBytes;
+    static constexpr int kQStages = 2;
+    static constexpr int kDoStages = (D == 64) ? 2 : 1;
+    static constexpr int kDsBytes = 2 * kAtomBytes;  // 128 key rows x 128 queries, bf16
+    static constexpr int kSmemBytes = kTileBytes * (2 + kQStages + kDoStages) + kDsBytes + 1024;
+    static constexpr bool kDqAliased = (D == 128);
+    static constexpr uint32_t kTmemCols = 512;
+    static constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
+    static constexpr uint32_t kColDQ = kDqAliased ? kColDP : (256 + 2 * D);
+};
+
+struct BwdBarriers {
+    uint64_t k_full, v_full;
+    uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+    uint64_t s_full, dp_full, p_ready, ds_ready, dq_full, dq_empty;
+};
+
+template <int D, bool GRADS_F32>
+__global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_constant__ TcBwdArgs a) {
+    using Cfg = BwdCfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sK = smem;
+    uint8_t* sV = sK + Cfg::kTileBytes;
+    uint8_t* sQ = sV + Cfg::kTileBytes;
+    uint8_t* sDO = sQ + Cfg::kQStages * Cfg::kTileBytes;
+    uint8_t* sDS = sDO + Cfg::kDoStages * Cfg::kTileBytes;
+
+    __shared__ BwdBarriers bars;
+    __shared__ __align__(16) float s_lse[2][kBQ];
+    __shared__ __align__(16) float s_D[2][kBQ];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t abort_flag;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    const int n_tiles = (a.T + kBKV - 1) / kBKV;
+    const int bh = blockIdx.x / n_tiles;
+    const int jt = blockIdx.x % n_tiles;  // key tile; tile 0 sees every query tile and goes first
+    const int n_it = n_tiles - jt;        // query tiles jt .. n_tiles-1
+
+    if (tid == 0) {
+        mbar_init(&bars.k_full, 1);
+        mbar_init(&bars.v_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars.q_full[s], 1);
+            mbar_init(&bars.q_empty[s], 1);
+            mbar_init(&bars.do_full[s], 1);
+            mbar_init(&bars.do_empty[s], 1);
+        }
+        mbar_init(&bars.s_full, 1);
+        mbar_init(&bars.dp_full, 1);
+        mbar_init(&bars.p_ready, kComputeThreads);
+        mbar_init(&bars.ds_ready, kComputeThreads);
+        mbar_init(&bars.dq_full, 1);
+        mbar_init(&bars.dq_empty, kComputeThreads);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(&tmem_base_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_slot;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&a.map_q);
+            tma_prefetch_desc(&a.map_k);
+            tma_prefetch_desc(&a.map_v);
+            tma_prefetch_desc(&a.map_do);
+            mbar_expect_tx(&bars.k_full, Cfg::kTileBytes);
+            for (int at = 0; at < Cfg::kAtoms; ++at)
+                tma_load_3d(sK + at * kAtomBytes, &a.map_k, &bars.k_full, at * 64, jt * kBKV, bh);
+            mbar_expect_tx(&bars.v_full, Cfg::kTileBytes);
+            for (int at = 0; at < Cfg::kAtoms; ++at)
+                tma_load_3d(sV + at * kAtomBytes, &a.map_v, &bars.v_full, at * 64, jt * kBKV, bh);
+            for (int it = 0; it < n_it; ++it) {
+                const int i = jt + it;
+                const int qs = it % Cfg::kQStages;
+                if (it >= Cfg::kQStages)
+                    mbar_wait(&bars.q_empty[qs], (it / Cfg::kQStages - 1) & 1, &abort_flag, a.fault_word, 0x40);
+                mbar_expect_tx(&bars.q_full[qs], Cfg::kTileBytes);
+                for (int at = 0; at < Cfg::kAtoms; ++at)
+                    tma_load_3d(sQ + qs * Cfg::kTileBytes + at * kAtomBytes, &a.map_q, &bars.q_full[qs], at * 64, i * kBQ, bh);
+                const int os = it % Cfg::kDoStages;
+                if (it >= Cfg::kDoStages)
+                    mbar_wait(&bars.do_empty[os], (it / Cfg::kDoStages - 1) & 1, &abort_flag, a.fault_word, 0x41);
+                mbar_expect_tx(&bars.do_full[os], Cfg::kTileBytes);
+                for (int at = 0; at < Cfg::kAtoms; ++at)
+                    tma_load_3d(sDO + os * Cfg::kTileBytes + at * kAtomBytes, &a.map_do, &bars.do_full[os], at * 64, i * kBQ, bh);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_st = make_idesc_bf16(kBKV, kBQ, 0, 0);  // S^T, dP^T
+        constexpr uint32_t idesc_kv = make_idesc_bf16(kBKV, D, 0, 1);    // dV, dK: B is MN-major
+        constexpr uint32_t idesc_dq = make_idesc_bf16(kBQ, D, 1, 1);     // dQ: A and B MN-major
+        const uint64_t k_kmaj = make_smem_desc_sw128(smem_u32(sK), 0, 1024);
+        const uint64_t v_kmaj = make_smem_desc_sw128(smem_u32(sV), 0, 1024);
+        const uint64_t k_mnmaj = make_smem_desc_sw128(smem_u32(sK), kAtomBytes, 1024);
+        const uint64_t ds_kmaj = make_smem_desc_sw128(smem_u32(sDS), 0, 1024);
+        const uint64_t ds_mnmaj = make_smem_desc_sw128(smem_u32(sDS), kAtomBytes, 1024);
+
+        auto issue_st = [&](int it) {  // S^T(it) = K_j Q^T
+            const int qs = it % Cfg::kQStages;
+            mbar_wait(&bars.q_full[qs], (it / Cfg::kQStages) & 1, &abort_flag, a.fault_word, 0x50);
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t q_kmaj = make_smem_desc_sw128(smem_u32(sQ + qs * Cfg::kTileBytes), 0, 1024);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
+                    tc_mma_ss(tmem + Cfg::kColS, desc_advance(k_kmaj, off), desc_advance(q_kmaj, off), idesc_st, kk > 0);
+                }
+                tc_commit(&bars.s_full);
+            }
+            __syncwarp();
+        };
+        auto issue_dp = [&](int it) {  // dP^T(it) = V_j dO^T
+            const int os = it % Cfg::kDoStages;
+            mbar_wait(&bars.do_full[os], (it / Cfg::kDoStages) & 1, &abort_flag, a.fault_word, 0x51);
+            if (Cfg::kDqAliased && it > 0)  // the dQ partial of the previous tile sits in these columns
+                mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x52);
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t do_kmaj = make_smem_desc_sw128(smem_u32(sDO + os * Cfg::kTileBytes), 0, 1024);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
+                    tc_mma_ss(tmem + Cfg::kColDP, desc_advance(v_kmaj, off), desc_advance(do_kmaj, off), idesc_st, kk > 0);
+                }
+                tc_commit(&bars.dp_full);
+            }
+            __syncwarp();
+        };
+
+        mbar_wait(&bars.k_full, 0, &abort_flag, a.fault_word, 0x53);
+        mbar_wait(&bars.v_full, 0, &abort_flag, a.fault_word, 0x54);
+        issue_st(0);
+        issue_dp(0);
+        for (int it = 0; it < n_it; ++it) {
+            const int qs = it % Cfg::kQStages;
+            const int os = it % Cfg::kDoStages;
+            // dV += P^T dO
+            mbar_wait(&bars.p_ready, it & 1, &abort_flag, a.fault_word, 0x55);
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t do_mnmaj = make_smem_desc_sw128(smem_u32(sDO + os * Cfg::kTileBytes), kAtomBytes, 1024);
+#pragma unroll
+                for (int kk = 0; kk < kBQ / 16; ++kk)
+                    tc_mma_ts(tmem + Cfg::kColDV, tmem + Cfg::kColS + kk * 8, desc_advance(do_mnmaj, kk * 2048), idesc_kv,
+                              (it > 0) || (kk > 0));
+                tc_commit(&bars.do_empty[os]);  // dP^T(it) and dV(it) were the readers of this dO tile
+            }
+            __syncwarp();
+            if (it + 1 < n_it) issue_st(it + 1);  // overlaps the exponentials of the next tile with dK/dQ of this one
+            // dK += dS^T Q ; dQ = dS K
+            mbar_wait(&bars.ds_ready, it & 1, &abort_flag, a.fault_word, 0x56);
+            if (!Cfg::kDqAliased && it > 0)  // previous dQ partial must have been read out of its columns
+                mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x57);
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t q_mnmaj = make_smem_desc_sw128(smem_u32(sQ + qs * Cfg::kTileBytes), kAtomBytes, 1024);
+#pragma unroll
+                for (int kk = 0; kk < kBQ / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
+                    tc_mma_ss(tmem + Cfg::kColDK, desc_advance(ds_kmaj, off), desc_advance(q_mnmaj, kk * 2048), idesc_kv,
+                              (it > 0) || (kk > 0));
+                }
+                tc_commit(&bars.q_empty[qs]);  // S^T(it) and dK(it) were the readers of this Q tile
+#pragma unroll
+                for (int kk = 0; kk < kBKV / 16; ++kk)
+                    tc_mma_ss(tmem + Cfg::kColDQ, desc_advance(ds_mnmaj, kk * 2048), desc_advance(k_mnmaj, kk * 2048),
+                              idesc_dq, kk > 0);
+                tc_commit(&bars.dq_full);
+            }
+            __syncwarp();
+            if (it + 1 < n_it) issue_dp(it + 1);
+        }
+    } else {
+        // ------------------------------------------------------------ compute warps: thread r = key row r
+        const int r = tid;
+        const uint32_t lane_base = uint32_t(warp) * 32u;
+        const float scale_log2 = a.scale * kLog2e;
+        const long long stat_base = (long long)bh * a.T;
+
+        auto drain_dq = [&](int it) {  // add the dQ partial of query tile jt+it to the FP32 accumulator
+            mbar_wait(&bars.dq_full, it & 1, &abort_flag, a.fault_word, 0x60);
+            tc_fence_after();
+            const int q_g = (jt + it) * kBQ + r;  // here thread r owns QUERY row r of the dQ tile
+            float* dst = a.dq_acc + (stat_base + q_g) * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDQ + c), v);
+                tmem_wait_ld();
+                if (q_g < a.T) {
+#pragma unroll
+                    for (int x = 0; x < 32; x += 4)
+                        red_add_v4(dst + c + x, __uint_as_float(v[x]), __uint_as_float(v[x + 1]), __uint_as_float(v[x + 2]),
+                                   __uint_as_float(v[x + 3]));
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&bars.dq_empty);
+        };
+
+        for (int it = 0; it < n_it; ++it) {
+            const int i = jt + it;
+            const int buf = it & 1;
+            {   // per-query statistics of this tile: column c of the transposed tiles is query i*128 + c
+                const int q_g = i * kBQ + r;
+                s_lse[buf][r] = (q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY;  // +inf -> P = 0
+                s_D[buf][r] = (q_g < a.T) ? a.D[stat_base + q_g] : 0.f;
+            }
+            named_bar_sync(1, kComputeThreads);
+
+            // ---- P^T
+            mbar_wait(&bars.s_full, it & 1, &abort_flag, a.fault_word, 0x61);
+            tc_fence_after();
+            float p[kBQ];
+            const bool diag = (i == jt);
+#pragma unroll
+            for (int c = 0; c < kBQ; c += 32) {
+                uint32_t sv[32];
+                tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColS + c), sv);
+                tmem_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int x = 0; x < 32; x += 4) {
+                    const float4 ls = *reinterpret_cast<const float4*>(&s_lse[buf][c + x]);
+                    const float l4[4] = {ls.x, ls.y, ls.z, ls.w};
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) {
+                        float e = fast_exp2(fmaf(__uint_as_float(sv[x + y]), scale_log2, -l4[y]));
+                        if (diag && (c + x + y) < r) e = 0.f;  // query before this key: masked
+                        p[c + x + y] = e;
+                    }
+                    pk[x >> 1] = pack_bf16x2(p[c + x], p[c + x + 1]);
+                    pk[(x >> 1) + 1] = pack_bf16x2(p[c + x + 2], p[c + x + 3]);
+                }
+                tmem_st16(tmem_addr(tmem, lane_base, Cfg::kColS + (c >> 1)), pk);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars.p_ready);
+
+            // ---- previous tile's dQ partial (its MMA ran while the exponentials above were computed)
+            if (it > 0) drain_dq(it - 1);
+
+            // ---- dS^T
+            mbar_wait(&bars.dp_full, it & 1, &abort_flag, a.fault_word, 0x62);
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < kBQ; c += 32) {
+                uint32_t dv[32];
+                tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDP + c), dv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 32; x += 8) {
+                    const float4 d0 = *reinterpret_cast<const float4*>(&s_D[buf][c + x]);
+                    const float4 d1 = *reinterpret_cast<const float4*>(&s_D[buf][c + x + 4]);
+                    const float dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+                    float ds[8];
+#pragma unroll
+                    for (int y = 0; y < 8; ++y) ds[y] = p[c + x + y] * (__uint_as_float(dv[x + y]) - dd[y]) * a.scale;
+                    uint4 w;
+                    w.x = pack_bf16x2(ds[0], ds[1]);
+                    w.y = pack_bf16x2(ds[2], ds[3]);
+                    w.z = pack_bf16x2(ds[4], ds[5]);
+                    w.w = pack_bf16x2(ds[6], ds[7]);
+                    const int qc = c + x;  // first query column of this 16-byte chunk
+                    *reinterpret_cast<uint4*>(sDS + (qc >> 6) * kAtomBytes + swz128(r, (qc & 63) >> 3)) = w;
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(&bars.ds_ready);
+        }
+        drain_dq(n_it - 1);  // dq_full of the last tile also means every dV / dK MMA has retired
+
+        // ---- epilogue: dV and dK of this key tile
+        const int kv_g = jt * kBKV + r;
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            const uint32_t col0 = which == 0 ? Cfg::kColDV : Cfg::kColDK;
+            void* gout = which == 0 ? a.dv : a.dk;
+            uint8_t* stage = sQ + which * Cfg::kTileBytes;  // Q stages are idle now
+#pragma unroll
+            for (int c = 0; c < D; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_addr(tmem, lane_base, col0 + c), v);
+                tmem_wait_ld();
+                if constexpr (GRADS_F32) {
+                    if (kv_g < a.T) {
+                        float* dst = reinterpret_cast<float*>(gout) + (stat_base + kv_g) * D + c;
+#pragma unroll
+                        for (int x = 0; x < 32; x += 4)
+                            *reinterpret_cast<float4*>(dst + x) =
+                                make_float4(__uint_as_float(v[x]), __uint_as_float(v[x + 1]), __uint_as_float(v[x + 2]),
+                                            __uint_as_float(v[x + 3]));
+                    }
+                } else {
+                    uint8_t* atom = stage + (c >> 6) * kAtomBytes;
+#pragma unroll
+                    for (int x = 0; x < 32; x += 8) {
+                        uint4 w;
+                        w.x = pack_bf16x2(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                        w.y = pack_bf16x2(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                        w.z = pack_bf16x2(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                        w.w = pack_bf16x2(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+                        *reinterpret_cast<uint4*>(atom + swz128(r, ((c & 63) + x) >> 3)) = w;
+                    }
+                }
+            }
+        }
+        if constexpr (!GRADS_F32) {
+            fence_proxy_async_smem();
+            named_bar_sync(1, kComputeThreads);
+            if (tid == 0) {
+                for (int at = 0; at < Cfg::kAtoms; ++at) {
+                    tma_store_3d(&a.map_dv, sQ + at * kAtomBytes, at * 64, jt * kBKV, bh);
+                    tma_store_3d(&a.map_dk, sQ + Cfg::kTileBytes + at * kAtomBytes, at * 64, jt * kBKV, bh);
+                }
+                tma_store_commit();
+                tma_store_wait_all();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem, Cfg::kTmemCols);
+}
+
+// ------------------------------------------------------------------ pre-pass
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+// One warp per row: D[row] = sum_e dO*O (16-byte loads), lse2[row] = log-sum-exp in log2 units.
+template <typename TIn>
+__global__ void __launch_bounds__(256) bwd_prepass_kernel(const TIn* __restrict__ o, const TIn* __restrict__ dO,
+                                                         const float* __restrict__ m, const float* __restrict__ l,
+                                                         const float* __restrict__ lse, float* __restrict__ Dout,
+                                                         float* __restrict__ lse2, long long rows, int d) {
+    constexpr int VEC = 16 / sizeof(TIn);
+    const int lane = threadIdx.x & 31;
+    long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const TIn* a = o + row * d;
+    const TIn* b = dO + row * d;
+    float acc = 0.f;
+    for (int e = lane * VEC; e < d; e += 32 * VEC) {
+        uint4 ua = __ldg(reinterpret_cast<const uint4*>(a + e));
+        uint4 ub = __ldg(reinterpret_cast<const uint4*>(b + e));
+        const TIn* pa = reinterpret_cast<const TIn*>(&ua);
+        const TIn* pb = reinterpret_cast<const TIn*>(&ub);
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) acc = fmaf(to_f32(pa[x]), to_f32(pb[x]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        Dout[row] = acc;
+        if (lse2) lse2[row] = (lse ? lse[row] : (m[row] + logf(l[row]))) * kLog2e;
+    }
+}
+
+template <int D, bool GRADS_F32>
+cudaError_t launch_bwd(const TcBwdArgs& a, cudaStream_t stream) {
+    using Cfg = BwdCfg<D>;
+    auto kern = attn_bwd_tc_kernel<D, GRADS_F32>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    const int n_tiles = (a.T + kBKV - 1) / kBKV;
+    const long long blocks = (long long)n_tiles * a.BH;
+    kern<<<(unsigned int)blocks, kThreads, Cfg::kSmemBytes, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream) {
+    if (a.BH == 0 || a.T == 0) return cudaSuccess;
+    if (a.d == 64) return a.grads_are_f32 ? launch_bwd<64, true>(a, stream) : launch_bwd<64, false>(a, stream);
+    if (a.d == 128) return a.grads_are_f32 ? launch_bwd<128, true>(a, stream) : launch_bwd<128, false>(a, stream);
+    return cudaErrorInvalidValue;
+}
+
+template <typename TIn>
+cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse, float* D,
+                               float* lse2, long long rows, int d, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    unsigned int blocks = (unsigned int)((rows + 7) / 8);
+    bwd_prepass_kernel<TIn><<<blocks, 256, 0, stream>>>(o, dO, m, l, lse, D, lse2, rows, d);
+    return cudaGetLastError();
+}
+template cudaError_t launch_bwd_prepass<float>(const float*, const float*, const float*, const float*, const float*,
+                                              float*, float*, long long, int, cudaStream_t);
+template cudaError_t launch_bwd_prepass<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const float*,
+                                                      const float*, const float*, float*, float*, long long, int,
+                                                      cudaStream_t);
+
+cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {
+    return launch_f32_to_bf16(dq_acc, dq, n, stream);
+}
+
+}  // namespace b200attn

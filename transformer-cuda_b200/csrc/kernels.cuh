@@ -1,0 +1,81 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel translation units.
+// Every launcher enqueues on `stream` and returns the launch status; none allocates.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200attn {
+
+// ------------------------------------------------------------------ layout_kernels.cu
+// TOut is float or __nv_bfloat16 for the split, TIn likewise for the merges.
+template <typename TOut>
+cudaError_t launch_qkv_split(const float* qkv, TOut* q, TOut* k, TOut* v, int B, int T, int H, int d,
+                             cudaStream_t stream);
+template <typename TIn>
+cudaError_t launch_qkv_merge_grad(const TIn* dq, const TIn* dk, const TIn* dv, float* dqkv, int B, int T, int H, int d,
+                                  cudaStream_t stream);
+template <typename TIn>
+cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream);
+template <typename TOut>
+cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T, int d, cudaStream_t stream);
+cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream);
+cudaError_t launch_fill_normal_f32(float* dst, long long n, unsigned long long seed, long long offset,
+                                   cudaStream_t stream);
+cudaError_t launch_fill_normal_bf16(__nv_bfloat16* dst, long long n, unsigned long long seed, long long offset,
+                                    cudaStream_t stream);
+
+// ------------------------------------------------------------------ softmax_kernels.cu
+cudaError_t launch_causal_softmax_fwd(const float* scores, float* probs, long long rows, int T, float scale,
+                                      cudaStream_t stream);
+cudaError_t launch_causal_softmax_bwd(const float* dprobs, const float* probs, float* dscores, long long rows, int T,
+                                      float scale, cudaStream_t stream);
+
+// ------------------------------------------------------------------ attn_f32.cu (SIMT FP32, parity mode)
+cudaError_t launch_attn_fwd_f32(const float* q, const float* k, const float* v, float* out, float* m_out, float* l_out,
+                                int BH, int T, int d, float scale, cudaStream_t stream);
+cudaError_t launch_dot_do_o_f32(const float* dO, const float* O, float* D, long long rows, int d, cudaStream_t stream);
+cudaError_t launch_attn_bwd_f32(const float* q, const float* k, const float* v, const float* dO, const float* m,
+                                const float* l, const float* D, float* dq, float* dk, float* dv, int BH, int T, int d,
+                                float scale, cudaStream_t stream);
+
+// ------------------------------------------------------------------ attn_tc_fwd.cu / attn_tc_bwd.cu (tcgen05)
+struct TcFwdArgs {
+    CUtensorMap map_q, map_k, map_v, map_o;  // (d, T, BH) BF16 tensors, box 64 x 128 x 1, 128-byte swizzle
+    void* out;                               // BF16 or FP32 (BH, T, d), selected by out_is_f32
+    int out_is_f32;
+    float* m_out;                            // optional (BH, T): row max of scaled scores
+    float* l_out;                            // optional (BH, T): sum exp(s - m)
+    float* lse_out;                          // optional (BH, T): m + log(l)
+    int BH, T, d;
+    float scale;
+    unsigned int* fault_word;
+};
+cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream);
+
+struct TcBwdArgs {
+    CUtensorMap map_q, map_k, map_v, map_do;  // BF16 (d, T, BH)
+    CUtensorMap map_dk, map_dv;               // BF16 outputs (used when grads_are_f32 == 0)
+    const float* lse2;                        // (BH, T) log-sum-exp in log2 units: lse * log2(e)
+    const float* D;                           // (BH, T) rowsum(dO * O)
+    float* dq_acc;                            // (BH, T, d) FP32, zeroed before launch, receives sum of partials
+    void* dk;                                 // BF16 or FP32 (BH, T, d)
+    void* dv;
+    int grads_are_f32;
+    int BH, T, d;
+    float scale;
+    unsigned int* fault_word;
+};
+cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream);
+
+// Backward pre-pass: D = rowsum(dO*O) and lse2 = (m + log l) * log2(e) or lse * log2(e).
+// TIn is float or __nv_bfloat16. Exactly one of (m,l) / lse is given.
+template <typename TIn>
+cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse,
+                               float* D, float* lse2, long long rows, int d, cudaStream_t stream);
+// dq (BF16) = dq_acc (FP32), elementwise.
+cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
+
+}  // namespace b200attn
