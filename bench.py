@@ -1,0 +1,327 @@
+#!/usr/bin/env python
+"""Benchmark of the causal attention path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c3|...]
+
+One "step" is one forward + backward pass of the attention core over one batch of seeded synthetic
+BF16 Q, K, V, dO ~ N(0,1). The default workload is the GPT-2-small shape of the benchmark spec
+(B=8, H=12, T=1024, d=64). With N > 1 (one process per GPU, launched by torchrun) every rank owns a
+contiguous range of (batch, head) slabs of a batch N times larger - the per-GPU work is fixed, no
+collective is on the data path, and the reported value is all ranks' FLOPs over the slowest rank's time.
+
+Rank 0 prints ONE JSON line. `value` is device-timed with inputs resident in HBM; `e2e` is the same
+metric through the public API with pinned HOST buffers, host<->device copies inside the timed region;
+`roofline` is the dominant kernel (the tcgen05 backward) against the measured dense-BF16 peak;
+`cpu_baseline` times the reference's own math (PyTorch, FP32, autograd) on the host cores.
+
+`--impl reference` runs only that CPU implementation, with all host threads, on the same workload
+definition (each step a bounded sample of it) and prints the same line with "impl": "reference".
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, T, d) per GPU
+    "c2": (8, 12, 1024, 64),      # GPT-2-small-shaped causal attention (the headline configuration)
+    "c3": (2, 16, 8192, 128),     # long context
+    "c5_512": (64, 32, 512, 128), "c5_1024": (32, 32, 1024, 128), "c5_2048": (16, 32, 2048, 128),
+    "c5_4096": (8, 32, 4096, 128), "c5_8192": (4, 32, 8192, 128), "c5_16384": (2, 32, 16384, 128),
+}
+METRIC = "causal_attention_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def flops(B, H, T, d):
+    """Algorithmic count, causal pairs as half the square: fwd 2*BH*T^2*d, bwd 5*BH*T^2*d."""
+    return 7.0 * B * H * T * T * d
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return dict(bf16=float(p["bf16_tflops"]), bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    except Exception:
+        return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def ncu_traffic_per_launch(workload):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if one covers this workload."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f).get(workload, {}).get("attn_bwd_tc_kernel_bytes_per_launch")
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc, self.path = None, f"/tmp/b200attn_clocks_{os.getpid()}.csv"
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.out,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def wait_first_sample(self, timeout_s=3.0):
+        t0 = time.perf_counter()
+        while self.proc is not None and time.perf_counter() - t0 < timeout_s:
+            try:
+                if os.path.getsize(self.path) > 0:
+                    break
+            except OSError:
+                pass
+            time.sleep(0.02)
+        self.t_region = time.perf_counter()
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 6 or not parts[0].isdigit():
+                    continue
+                sm.append(int(parts[0]))
+                mx.append(int(parts[1]))
+                for n, v in zip(names, parts[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return None
+        busy = [x for x in sm if x > 0.5 * max(sm)] or sm
+        return dict(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_baseline(B, H, T, d, budget_s):
+    """The reference's math on the host cores: PyTorch FP32 forward + autograd backward
+    (oracle/torch_port.py), all threads, on a bounded sample of the workload's slabs."""
+    import torch
+    from oracle import torch_port
+    torch.set_num_threads(os.cpu_count() or 1)
+    r = torch_port.time_forward_backward(B * H, T, d, budget_s=budget_s)
+    tf = flops(1, 1, T, d) / r["seconds_per_slab"] / 1e12
+    return dict(value=tf, unit=UNIT, cores=r["threads"], kind="port",
+                sample=f"{r['slabs_timed']} (batch,head) slab passes of the workload's {B * H} slabs, {r['slabs_per_call']} per "
+                       f"call, {r['calls']} calls after 1 warm-up, PyTorch FP32 forward + autograd backward")
+
+
+def run_reference(args, B, H, T, d):
+    """--impl reference: K timed steps of the CPU implementation, each a bounded sample (a few slabs)."""
+    import torch
+    from oracle import torch_port
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    per_step = max(1, min(8, B * H, (1 << 28) // (T * T)))
+    g = torch.Generator().manual_seed(0)
+    q, k, v, dO = (torch.randn(per_step, T, d, generator=g) for _ in range(4))
+    scale = 1.0 / math.sqrt(d)
+    for _ in range(args.warmup):
+        torch_port.forward_backward(q, k, v, dO, scale)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        torch_port.forward_backward(q, k, v, dO, scale)
+    el = time.perf_counter() - t0
+    tf = flops(1, per_step, T, d) * args.steps / el / 1e12
+    sample = f"{per_step} of {B * H} (batch,head) slabs per step, PyTorch FP32 autograd on host CPU"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args, B, H, T, d), "sample": sample},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def workload_name(args, B, H, T, d):
+    return f"{args.workload}: causal attention fwd+bwd, B={B} H={H} T={T} d={d} per GPU, BF16, scale=1/sqrt(d)"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-budget-s", type=float, default=12.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    B, H, T, d = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, B, H, T, d)
+        return
+
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    ops = pkg.ops
+    from transformer_cuda_b200 import dist as pdist
+
+    rank, world, local = pdist.init()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU fallback (use --impl reference for the CPU arm)")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+
+    # ---- weak scaling: the global batch is `world` times the per-GPU batch, split by (batch, head) slabs
+    total_slabs = B * H * world
+    mine = pkg.shard.slab_range(total_slabs, rank, world)
+    BH = mine.count
+    n = BH * T * d
+    scale = 1.0 / math.sqrt(d)
+    bf16 = torch.bfloat16
+    set_bytes = 9 * n * 2  # q,k,v,o,dO,dq,dk,dv in BF16 + about one tensor of scratch traffic
+    n_sets = max(2, math.ceil(2.0 * L2_BYTES / set_bytes))  # rotate so that a step's inputs were evicted from L2
+    sets = []
+    for s in range(n_sets):
+        ts = []
+        for i in range(4):  # q, k, v, dO: counter-based streams indexed by global element, distinct per set
+            t = torch.empty(BH, T, d, device=dev, dtype=bf16)
+            ops.fill_normal_(t, seed=1000 + 10 * s + i, offset=pkg.shard.element_offset(mine, T, d))
+            ts.append(t)
+        q, k, v, dO = ts
+        sets.append(dict(q=q, k=k, v=v, dO=dO, o=torch.empty_like(q), lse=torch.empty(BH, T, device=dev),
+                         dq=torch.empty_like(q), dk=torch.empty_like(q), dv=torch.empty_like(q)))
+    ops.reserve(BH, T, d)
+
+    def step(s):
+        ops.attention_forward_bf16(s["q"], s["k"], s["v"], scale, s["o"], s["lse"])
+        ops.attention_backward_bf16(s["q"], s["k"], s["v"], s["o"], s["dO"], s["lse"], scale, s["dq"], s["dk"], s["dv"])
+
+    sampler = ClockSampler(local) if rank == 0 else None  # started early: nvidia-smi needs a moment to come up
+    for i in range(args.warmup):
+        step(sets[i % n_sets])
+    torch.cuda.synchronize()
+    ops.check_device_fault()
+    if sampler:
+        sampler.wait_first_sample()
+
+    # ---- device-timed region: exactly K steps between barrier + synchronize on both sides
+    ops.kernel_timing(True)
+    pdist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(sets[i % n_sets])
+    e1.record()
+    torch.cuda.synchronize()
+    pdist.barrier()
+    ms_total = pdist.max_over_ranks(e0.elapsed_time(e1), device=dev)
+    kt = ops.kernel_times()
+    ops.kernel_timing(False)
+    clocks = sampler.stop() if sampler else None
+    ops.check_device_fault()
+    ms_per_step = ms_total / args.steps
+    step_flops = flops(1, BH, T, d)
+    all_flops = pdist.sum_over_ranks(step_flops, device=dev)
+    value = all_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host buffers -> device -> forward + backward -> host, every step
+    host_in = [torch.empty(BH, T, d, dtype=bf16).pin_memory() for _ in range(4)]
+    for hbuf, key in zip(host_in, ("q", "k", "v", "dO")):
+        hbuf.copy_(sets[0][key])
+    host_out = [torch.empty(BH, T, d, dtype=bf16).pin_memory() for _ in range(4)]
+    e2e_set = sets[-1]
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        for hbuf, key in zip(host_in, ("q", "k", "v", "dO")):
+            e2e_set[key].copy_(hbuf, non_blocking=True)
+        step(e2e_set)
+        for hbuf, key in zip(host_out, ("o", "dq", "dk", "dv")):
+            hbuf.copy_(e2e_set[key], non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    pdist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    pdist.barrier()
+    e2e_ms = pdist.max_over_ranks(max(e0.elapsed_time(e1), wall_ms), device=dev) / e2e_steps
+    e2e_value = all_flops / (e2e_ms * 1e-3) / 1e12
+
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    bwd_ms = kt["bwd_ms"] / max(1, kt["bwd_launches"])
+    fwd_ms = kt["fwd_ms"] / max(1, kt["fwd_launches"])
+    bwd_tf = 5.0 * BH * T * T * d / (bwd_ms * 1e-3) / 1e12 if bwd_ms > 0 else 0.0
+    fwd_tf = 2.0 * BH * T * T * d / (fwd_ms * 1e-3) / 1e12 if fwd_ms > 0 else 0.0
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload_name(args, B, H, T, d), "global_batch": B * world,
+                   "sharding": f"(batch,head) slabs, {B * H} per GPU, no collective",
+                   "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * set_bytes >> 20} MiB > L2) so a step reads from HBM",
+                   "flops_per_step_per_gpu": step_flops},
+        "frac_of_bf16_peak": value / world / peaks["bf16"],
+        "tokens_per_s": B * world * T / (ms_per_step * 1e-3),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * n * 2, "d2h_bytes_per_step": 4 * n * 2,
+                "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "path": "pinned host BF16 q,k,v,dO -> device -> b200attn_fwd_bf16 + b200attn_bwd_bf16 -> host o,dq,dk,dv"},
+        "gpu_launches": 4 * args.steps,  # per step: forward kernel, backward pre-pass, backward kernel, dQ convert
+        "roofline": {"bound": "tensor", "kernel": "attn_bwd_tc_kernel", "achieved": bwd_tf, "peak": peaks["bf16"],
+                     "unit": UNIT, "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} (burst cuBLAS BF16)",
+                     "traffic": ncu_traffic_per_launch(args.workload), "launch_ms": bwd_ms,
+                     "flops_per_launch": 5.0 * BH * T * T * d,
+                     "forward_kernel": {"kernel": "attn_fwd_tc_kernel", "achieved": fwd_tf, "launch_ms": fwd_ms,
+                                        "frac": fwd_tf / peaks["bf16"]}},
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:  # the CPU arm runs beside the 1-GPU measurement only
+        line["cpu_baseline"] = cpu_baseline(B, H, T, d, args.cpu_budget_s)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -51,6 +51,15 @@ int b200attn_release(void);
  * waits ran out (0 = none); clears the word. `code` is a HOST pointer and may be NULL. */
 int b200attn_check_device_fault(unsigned int* code);
 
+/* Per-launch timing of the two tensor-core kernels, for roofline reporting: while enabled, every
+ * launch of the forward / backward tcgen05 kernel is bracketed by CUDA events on its stream
+ * (not to be enabled while capturing a graph). Enabling or disabling clears earlier records.
+ * b200attn_kernel_times waits for the recorded launches and returns the summed durations in
+ * milliseconds and the launch counts (HOST pointers, any may be NULL). No reference counterpart:
+ * the reference times whole phases with its GpuTimer (include/common.h:35-62). */
+int b200attn_kernel_timing(int enable);
+int b200attn_kernel_times(double* fwd_ms_total, int* fwd_launches, double* bwd_ms_total, int* bwd_launches);
+
 /* ------------------------------------------------------------------ FP32 API (drop-in) -------- */
 /* (B,T,3*H*d) -> q,k,v (B,H,T,d).  Replaces qkv_split_transpose_forward,
  * include/kernels/attention.cuh:6, src/kernels/attention.cu:381. */

@@ -91,3 +91,15 @@ def test_bf16_round_matches_torch():
     x = np.random.default_rng(1).standard_normal(4096).astype(np.float32) * 3
     want = torch.from_numpy(x).to(torch.bfloat16).to(torch.float32).numpy()
     assert np.array_equal(orc.bf16_round(x), want)
+
+
+def test_torch_port_agrees_with_numpy_oracle():
+    import torch
+    from oracle import torch_port
+    rng = np.random.default_rng(5)
+    q, k, v, dO = (rng.standard_normal((3, 70, 32)).astype(np.float32) for _ in range(4))
+    scale = 1 / math.sqrt(32)
+    out, dq, dk, dv = torch_port.forward_backward(*(torch.from_numpy(a) for a in (q, k, v, dO)), scale)
+    ref = orc.attention_forward_backward(q, k, v, dO, scale)
+    for got, key in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert orc.compute_metrics(got.numpy(), ref[key])["max_abs"] <= TOL, key

@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "../../include/b200attn.h"
 #include "kernels.cuh"
@@ -53,6 +54,33 @@ struct DeviceState {
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mutex;
+
+// Optional per-launch timing of the two tensor-core kernels (CUDA events on the launching stream).
+struct TimedLaunch {
+    cudaEvent_t start, stop;
+    int kind;  // 0 forward kernel, 1 backward kernel
+};
+std::atomic<int> g_timing_enabled{0};
+std::vector<TimedLaunch> g_timed;
+std::mutex g_timed_mutex;
+
+struct ScopedKernelTimer {
+    cudaStream_t stream;
+    TimedLaunch t{};
+    bool active = false;
+    ScopedKernelTimer(int kind, cudaStream_t s) : stream(s) {
+        if (!g_timing_enabled.load()) return;
+        if (cudaEventCreate(&t.start) != cudaSuccess || cudaEventCreate(&t.stop) != cudaSuccess) return;
+        t.kind = kind;
+        active = cudaEventRecord(t.start, stream) == cudaSuccess;
+    }
+    ~ScopedKernelTimer() {
+        if (!active) return;
+        cudaEventRecord(t.stop, stream);
+        std::lock_guard<std::mutex> lock(g_timed_mutex);
+        g_timed.push_back(t);
+    }
+};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -184,6 +212,7 @@ int run_fwd_tc(DeviceState* st, const void* q, const void* k, const void* v, voi
     a.BH = BH, a.T = T, a.d = d;
     a.scale = scale;
     a.fault_word = st->fault_word;
+    ScopedKernelTimer timer(0, stream);
     RETURN_IF_CUDA(launch_attn_fwd_tc(a, stream), "tensor-core forward launch");
     return B200ATTN_OK;
 }
@@ -211,6 +240,7 @@ int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, con
     a.BH = BH, a.T = T, a.d = d;
     a.scale = scale;
     a.fault_word = st->fault_word;
+    ScopedKernelTimer timer(1, stream);
     RETURN_IF_CUDA(launch_attn_bwd_tc(a, stream), "tensor-core backward launch");
     return B200ATTN_OK;
 }
@@ -263,6 +293,35 @@ extern "C" int b200attn_check_device_fault(unsigned int* code) {
         RETURN_IF_CUDA(cudaMemset(st->fault_word, 0, sizeof(w)), "cudaMemset(fault word)");
         return fail(B200ATTN_ERR_DEVICE_FAULT, "a bounded wait inside a kernel ran out (fault word 0x%08x)", w);
     }
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_kernel_timing(int enable) {
+    std::lock_guard<std::mutex> lock(g_timed_mutex);
+    for (auto& t : g_timed) {
+        cudaEventDestroy(t.start);
+        cudaEventDestroy(t.stop);
+    }
+    g_timed.clear();
+    g_timing_enabled.store(enable ? 1 : 0);
+    return B200ATTN_OK;
+}
+
+extern "C" int b200attn_kernel_times(double* fwd_ms_total, int* fwd_launches, double* bwd_ms_total, int* bwd_launches) {
+    std::lock_guard<std::mutex> lock(g_timed_mutex);
+    double tot[2] = {0.0, 0.0};
+    int cnt[2] = {0, 0};
+    for (auto& t : g_timed) {
+        RETURN_IF_CUDA(cudaEventSynchronize(t.stop), "cudaEventSynchronize");
+        float ms = 0.f;
+        RETURN_IF_CUDA(cudaEventElapsedTime(&ms, t.start, t.stop), "cudaEventElapsedTime");
+        tot[t.kind] += ms;
+        cnt[t.kind] += 1;
+    }
+    if (fwd_ms_total) *fwd_ms_total = tot[0];
+    if (fwd_launches) *fwd_launches = cnt[0];
+    if (bwd_ms_total) *bwd_ms_total = tot[1];
+    if (bwd_launches) *bwd_launches = cnt[1];
     return B200ATTN_OK;
 }
 

@@ -1,0 +1,71 @@
+"""Process-level plumbing for running the (batch, head)-sharded path on several GPUs of one box:
+rank discovery from the torchrun environment, the barrier + max-over-ranks timing reduction the
+benchmark uses, and a gather of per-shard results for tests. The attention path itself exchanges
+nothing between ranks; the only collectives here carry timings and test data."""
+import os
+
+import torch
+import torch.distributed as dist
+
+from .shard import slab_range
+
+
+def env_rank_world():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def init(backend=None):
+    """Join the process group described by RANK / WORLD_SIZE / MASTER_* (no-op for a single process)."""
+    rank, world, local = env_rank_world()
+    if world > 1 and not dist.is_initialized():
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kwargs = {}
+        if backend == "nccl":
+            kwargs["device_id"] = torch.device("cuda", local)
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
+    return rank, world, local
+
+
+def barrier():
+    if dist.is_initialized():
+        dist.barrier()
+
+
+def max_over_ranks(value: float, device="cpu") -> float:
+    """The slowest rank's value: multi-GPU times are reported as the maximum over ranks."""
+    if not dist.is_initialized():
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(value: float, device="cpu") -> float:
+    if not dist.is_initialized():
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def my_slabs(total_slabs: int):
+    rank, world, _ = env_rank_world()
+    if dist.is_initialized():
+        rank, world = dist.get_rank(), dist.get_world_size()
+    return slab_range(total_slabs, rank, world)
+
+
+def gather_slabs(local: torch.Tensor, total_slabs: int) -> torch.Tensor:
+    """Concatenate per-rank (count_r, ...) tensors into the full (total_slabs, ...) tensor on every rank."""
+    if not dist.is_initialized():
+        return local
+    world = dist.get_world_size()
+    tail = tuple(local.shape[1:])
+    counts = [slab_range(total_slabs, r, world).count for r in range(world)]
+    width = max(counts)  # all_gather wants equal shapes: pad every shard to the largest one
+    padded = torch.zeros((width,) + tail, dtype=local.dtype, device=local.device)
+    padded[: local.shape[0]] = local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded)
+    return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)

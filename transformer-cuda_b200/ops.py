@@ -191,3 +191,17 @@ def fill_normal_(t, seed, offset=0):
     else:
         _lib.call("b200attn_fill_normal_bf16", _ptr(t, BF16, "dst"), t.numel(), int(seed), int(offset), _stream())
     return t
+
+
+def kernel_timing(enable):
+    """Start (True) or stop (False) per-launch event timing of the tensor-core kernels; clears records."""
+    _lib.call("b200attn_kernel_timing", 1 if enable else 0)
+
+
+def kernel_times():
+    """Summed durations and launch counts recorded since kernel_timing(True):
+    dict(fwd_ms, fwd_launches, bwd_ms, bwd_launches)."""
+    f, b = ctypes.c_double(0), ctypes.c_double(0)
+    nf, nb = ctypes.c_int(0), ctypes.c_int(0)
+    _lib.call("b200attn_kernel_times", ctypes.byref(f), ctypes.byref(nf), ctypes.byref(b), ctypes.byref(nb))
+    return dict(fwd_ms=f.value, fwd_launches=nf.value, bwd_ms=b.value, bwd_launches=nb.value)
