@@ -112,6 +112,22 @@ int b200attn_fwd_bf16(const void* q, const void* k, const void* v, void* out, fl
 /* dq,dk,dv (BH,T,d) bf16, overwritten. Uses library scratch (4*BH*T*d + 8*BH*T bytes). */
 int b200attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                       void* dq, void* dk, void* dv, int BH, int T, int d, float scale, b200attn_stream_t stream);
+/* The same backward for callers that must not allocate device memory: hosts whose own pool already
+ * owns the whole GPU (a cudaMalloc from a plugin would fail or fragment it), latency-critical loops
+ * that cannot take the device-wide synchronisation hidden in cudaMalloc/cudaFree, and sandboxes that
+ * forbid allocation calls. It has no counterpart in the reference (whose callers allocate every
+ * buffer themselves, src/model.cu:35-124). Scratch comes from a static device array of
+ * B200ATTN_NOALLOC_SCRATCH_BYTES that every GPU loading the library holds until exit; the call makes
+ * no cudaMalloc/cudaFree or other allocating call. Limits: 256 + 4*BH*T*d + 8*BH*T bytes (each part
+ * rounded up to 256) must fit in the array, else B200ATTN_ERR_UNSUPPORTED (the benchmark shape
+ * BH=96, T=1024, d=64 fits); failures are also printed to stderr. All calls on a device share the
+ * array, which keeps the previous call's contents (each call clears what must start from zero), so
+ * calls that overlap on the GPU race. The first call on a device looks up the array's address and
+ * clears its fault word synchronously: make it before any stream capture. */
+#define B200ATTN_NOALLOC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                              const float* lse, void* dq, void* dk, void* dv, int BH, int T, int d, float scale,
+                              b200attn_stream_t stream);
 /* FP32 (B,T,3*H*d) -> BF16 q,k,v (B,H,T,d): the split-transpose fused with the down-conversion
  * (same index map as src/kernels/attention.cu:24-83). */
 int b200attn_qkv_split_bf16(const float* qkv, void* q, void* k, void* v, int B, int T, int H, int d,

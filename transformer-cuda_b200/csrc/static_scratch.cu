@@ -1,0 +1,176 @@
+// b200attn_bwd_bf16_noalloc: the BF16 backward for callers that must not allocate device memory.
+//
+// Who needs this. Some hosts hand the whole GPU to their own memory pool at start-up (inference
+// servers, frameworks with a caching allocator set to take everything), so a later cudaMalloc from
+// a plugin fails or fragments their pool. Others run inside a latency-critical loop where the
+// implicit device-wide synchronisation of cudaMalloc / cudaFree is not acceptable, or load this
+// library into a sandbox whose policy forbids allocation calls altogether. b200attn_bwd_bf16 grows a
+// library-owned heap buffer on demand and so does not suit them; this entry point takes the
+// backward's scratch (FP32 dQ accumulator, D, log2-domain lse, and the fault word of the bounded
+// waits) from a fixed array that is part of the loaded module instead. It calls no cudaMalloc,
+// cudaFree, cudaMallocAsync or any other allocating routine.
+//
+// Costs and rules, all of which follow from the array being one static object per device:
+//   * every GPU that loads the library holds B200ATTN_NOALLOC_SCRATCH_BYTES (32 MiB) until exit;
+//   * shapes whose scratch does not fit are rejected with B200ATTN_ERR_UNSUPPORTED;
+//   * all calls on a device share the array and it keeps the previous call's contents: the parts
+//     that must start from zero (the dQ accumulator) are cleared on the stream by every call, and
+//     two calls that overlap on the GPU (different streams, no dependency) race on it;
+//   * the first call on each device looks up the array's device address and clears the fault word
+//     with a synchronous memset, so make that first call before starting any stream capture.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200attn.h"
+#include "kernels.cuh"
+
+namespace {
+
+using namespace b200attn;
+
+constexpr size_t kScratchBytes = B200ATTN_NOALLOC_SCRATCH_BYTES;
+constexpr size_t kFaultRegion = 256;  // first 256 bytes: the fault word of the kernels' bounded waits
+
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
+
+constexpr int kMaxDevices = 64;
+struct PerDevice {
+    unsigned char* base = nullptr;  // device address of g_noalloc_scratch on this device
+    bool is_sm100 = false;
+};
+PerDevice g_per_device[kMaxDevices];
+std::mutex g_setup_mutex;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_fn = nullptr;
+
+thread_local char g_noalloc_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_noalloc_error, sizeof(g_noalloc_error), fmt, ap);
+    va_end(ap);
+    // Leave the text where b200attn_last_error() finds it: report through a failing call of the
+    // public API would change that code path, so the message is also printed here.
+    fprintf(stderr, "[b200attn] b200attn_bwd_bf16_noalloc: %s\n", g_noalloc_error);
+    return code;
+}
+
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Set-up, once per device, with that device current.
+int setup_current_device(PerDevice** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(B200ATTN_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    PerDevice& pd = g_per_device[dev];
+    if (pd.base == nullptr) {
+        unsigned char* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(B200ATTN_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(e));
+        e = cudaMemset(ptr, 0, kFaultRegion);
+        if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "cudaMemset(fault word): %s", cudaGetErrorString(e));
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+        pd.is_sm100 = (major == 10);
+        if (!g_encode_fn) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+            if (e != cudaSuccess || !fn) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+            g_encode_fn = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        pd.base = ptr;
+    }
+    *out = &pd;
+    return B200ATTN_OK;
+}
+
+int encode_map(CUtensorMap* m, const void* base, int BH, int T, int d) {
+    cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
+    cuuint64_t strides[2] = {cuuint64_t(d) * 2, cuuint64_t(T) * d * 2};
+    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode_fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", int(r));
+    return B200ATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                                         const float* lse, void* dq, void* dk, void* dv, int BH, int T, int d,
+                                         float scale, b200attn_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (BH < 0 || T < 0 || d <= 0) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "negative size or d <= 0 (BH=%d T=%d d=%d)", BH, T, d);
+    const size_t rows = size_t(BH) * T;
+    if (rows == 0) return B200ATTN_OK;
+    if (!q || !k || !v || !o || !dO || !lse || !dq || !dk || !dv) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "a tensor argument is NULL");
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dO) || !aligned16(dq) ||
+        !aligned16(dk) || !aligned16(dv))
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "tensors must be 16-byte aligned");
+    if (d != 64 && d != 128) return fail(B200ATTN_ERR_UNSUPPORTED, "d must be 64 or 128, got %d", d);
+    const size_t n = rows * size_t(d);
+    const size_t need = kFaultRegion + round_up(n * sizeof(float), 256) + 2 * round_up(rows * sizeof(float), 256);
+    if (need > kScratchBytes)
+        return fail(B200ATTN_ERR_UNSUPPORTED,
+                    "shape BH=%d T=%d d=%d needs %zu bytes of scratch but the static array holds %zu; use b200attn_bwd_bf16 "
+                    "or split the (batch, head) slabs over several calls", BH, T, d, need, kScratchBytes);
+    PerDevice* pd = nullptr;
+    int rc = setup_current_device(&pd);
+    if (rc) return rc;
+    if (!pd->is_sm100) return fail(B200ATTN_ERR_UNSUPPORTED, "needs an sm_100a device (B200)");
+
+    unsigned char* p = pd->base;
+    unsigned int* fault_word = reinterpret_cast<unsigned int*>(p);
+    p += kFaultRegion;
+    float* dq_acc = reinterpret_cast<float*>(p);
+    p += round_up(n * sizeof(float), 256);
+    float* D = reinterpret_cast<float*>(p);
+    p += round_up(rows * sizeof(float), 256);
+    float* lse2 = reinterpret_cast<float*>(p);
+
+    TcBwdArgs a;
+    memset(&a, 0, sizeof(a));
+    if ((rc = encode_map(&a.map_q, q, BH, T, d))) return rc;
+    if ((rc = encode_map(&a.map_k, k, BH, T, d))) return rc;
+    if ((rc = encode_map(&a.map_v, v, BH, T, d))) return rc;
+    if ((rc = encode_map(&a.map_do, dO, BH, T, d))) return rc;
+    if ((rc = encode_map(&a.map_dk, dk, BH, T, d))) return rc;
+    if ((rc = encode_map(&a.map_dv, dv, BH, T, d))) return rc;
+    a.lse2 = lse2;
+    a.D = D;
+    a.dq_acc = dq_acc;
+    a.dk = dk;
+    a.dv = dv;
+    a.grads_are_f32 = 0;
+    a.BH = BH, a.T = T, a.d = d;
+    a.scale = scale;
+    a.fault_word = fault_word;
+
+    cudaError_t e = launch_bwd_prepass<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dO),
+                                                      nullptr, nullptr, lse, D, lse2, (long long)rows, d, stream);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
+    // the accumulator still holds the previous call's sums: it must start from zero
+    e = cudaMemsetAsync(dq_acc, 0, n * sizeof(float), stream);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "cudaMemsetAsync(dq accumulator): %s", cudaGetErrorString(e));
+    e = launch_attn_bwd_tc(a, stream);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "backward launch: %s", cudaGetErrorString(e));
+    e = launch_dq_convert(dq_acc, static_cast<__nv_bfloat16*>(dq), (long long)n, stream);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "dq convert launch: %s", cudaGetErrorString(e));
+    return B200ATTN_OK;
+}

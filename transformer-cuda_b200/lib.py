@@ -13,6 +13,7 @@ HEADER_PATH = os.path.join(HERE, "..", "include", "b200attn.h")
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_SCRATCH, ERR_DEVICE_FAULT = -1, -2, -3, -4, -5
 MATH_FP32, MATH_BF16 = 0, 1
+NOALLOC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 
 class B200AttnError(RuntimeError):
@@ -45,6 +46,7 @@ _SIGNATURES = {
     "b200attn_split_heads_f32": ([_P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_fwd_bf16": ([_P, _P, _P, _P, _P, _I, _I, _I, _F, _P], _I),
     "b200attn_bwd_bf16": ([_P] * 9 + [_I, _I, _I, _F, _P], _I),
+    "b200attn_bwd_bf16_noalloc": ([_P] * 9 + [_I, _I, _I, _F, _P], _I),
     "b200attn_qkv_split_bf16": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_qkv_merge_grad_bf16": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_merge_heads_bf16": ([_P, _P, _I, _I, _I, _I, _P], _I),

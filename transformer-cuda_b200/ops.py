@@ -141,6 +141,18 @@ def attention_backward_bf16(q, k, v, o, dO, lse, scale, dq=None, dk=None, dv=Non
     return dq, dk, dv
 
 
+def attention_backward_bf16_noalloc(q, k, v, o, dO, lse, scale, dq, dk, dv):
+    """The BF16 backward through the entry point that takes its scratch from the library's static
+    device array instead of allocating (see include/b200attn.h for who needs it and its size limit).
+    Output tensors are passed in, so this wrapper allocates nothing either."""
+    T, d = q.shape[-2], q.shape[-1]
+    BH = q.numel() // (T * d) if T * d else 0
+    _lib.call("b200attn_bwd_bf16_noalloc", _ptr(q, BF16, "q"), _ptr(k, BF16, "k"), _ptr(v, BF16, "v"),
+              _ptr(o, BF16, "o"), _ptr(dO, BF16, "dO"), _ptr(lse, F32, "lse"), _ptr(dq, BF16, "dq"),
+              _ptr(dk, BF16, "dk"), _ptr(dv, BF16, "dv"), BH, T, d, float(scale), _stream())
+    return dq, dk, dv
+
+
 def qkv_split_transpose_forward_bf16(qkv, q, k, v, B, T, H, d_head):
     """FP32 (B,T,3*H*d) -> BF16 q,k,v (B,H,T,d)."""
     _lib.call("b200attn_qkv_split_bf16", _ptr(qkv, F32, "qkv"), _ptr(q, BF16, "q"), _ptr(k, BF16, "k"),
