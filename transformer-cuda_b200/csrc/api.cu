@@ -177,6 +177,19 @@ int make_map(CUtensorMap* m, const void* base, int BH, int T, int d) {
     return B200ATTN_OK;
 }
 
+// (d, T, BH) FP32 tensor viewed through 32 x 128 x 1 boxes (128 bytes per row) with the 128-byte swizzle.
+int make_map_f32(CUtensorMap* m, const void* base, int BH, int T, int d) {
+    cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
+    cuuint64_t strides[2] = {cuuint64_t(d) * 4, cuuint64_t(T) * d * 4};
+    cuuint32_t box[3] = {32, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled (FP32) failed with code %d (BH=%d T=%d d=%d)", int(r), BH, T, d);
+    return B200ATTN_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_dims4(const char* fn, int B, int H, int T, int d) {
@@ -231,6 +244,7 @@ int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, con
         if ((rc = make_map(&a.map_dk, dk, BH, T, d))) return rc;
         if ((rc = make_map(&a.map_dv, dv, BH, T, d))) return rc;
     }
+    if ((rc = make_map_f32(&a.map_dq_acc, dq_acc, BH, T, d))) return rc;
     a.lse2 = lse2;
     a.D = D;
     a.dq_acc = dq_acc;
@@ -451,9 +465,9 @@ extern "C" int b200attn_bwd_f32(const float* q, const float* k, const float* v, 
     RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
     RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
     RETURN_IF_CUDA(launch_f32_to_bf16(dO, dob, (long long)n, stream), "convert dO");
-    RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, rows, d, stream), "pre-pass");
-    // dq is the FP32 accumulator itself: partial sums are reduced straight into the caller's buffer
-    RETURN_IF_CUDA(cudaMemsetAsync(dq, 0, n * sizeof(float), stream), "cudaMemsetAsync(dq)");
+    // dq is the FP32 accumulator itself: partial sums are reduced straight into the caller's buffer,
+    // which the pre-pass clears
+    RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, dq, rows, d, stream), "pre-pass");
     return run_bwd_tc(st, qb, kb, vb, dob, lse2, workspace, dq, dk, dv, true, BH, T, d, scale, stream);
 }
 
@@ -521,8 +535,7 @@ extern "C" int b200attn_bwd_bf16(const void* q, const void* k, const void* v, co
     float* lse2 = bump.take<float>(size_t(rows));
     const __nv_bfloat16* ob = static_cast<const __nv_bfloat16*>(o);
     const __nv_bfloat16* dob = static_cast<const __nv_bfloat16*>(dO);
-    RETURN_IF_CUDA(launch_bwd_prepass<__nv_bfloat16>(ob, dob, nullptr, nullptr, lse, D, lse2, rows, d, stream), "pre-pass");
-    RETURN_IF_CUDA(cudaMemsetAsync(dq_acc, 0, n * sizeof(float), stream), "cudaMemsetAsync(dq accumulator)");
+    RETURN_IF_CUDA(launch_bwd_prepass<__nv_bfloat16>(ob, dob, nullptr, nullptr, lse, D, lse2, dq_acc, rows, d, stream), "pre-pass");
     if ((rc = run_bwd_tc(st, q, k, v, dO, lse2, D, dq_acc, dk, dv, false, BH, T, d, scale, stream))) return rc;
     RETURN_IF_CUDA(launch_dq_convert(dq_acc, static_cast<__nv_bfloat16*>(dq), (long long)n, stream), "dq convert");
     return B200ATTN_OK;

@@ -10,22 +10,42 @@
 //
 //   S^T  = K_j Q_i^T                  (SS MMA, both operands K-major)        -> TMEM
 //   dP^T = V_j dO_i^T                 (SS MMA)                               -> TMEM
-//   P^T  = exp2(S^T*scale*log2e - lse2[q])   written BF16 over S^T in TMEM
+//   P^T  = exp2(S^T*scale*log2e - lse2[q])   written BF16 over S^T in TMEM (queries 0-63 packed in
+//                                            columns [0,32), queries 64-127 in columns [64,96))
 //   dV  += P^T dO_i                   (TS MMA: A = P^T from TMEM, dO_i MN-major)
 //   dS^T = P^T * (dP^T - D[q]) * scale       written BF16 to shared memory, 128B-swizzled
 //   dK  += dS^T Q_i                   (SS MMA: A = dS^T K-major, Q_i MN-major)
 //   dQ_i = dS K_j                     (SS MMA: the same dS^T tile read as an MN-major A, K_j MN-major)
 //
-// dQ_i is a partial sum over key tiles: the compute warps read it from TMEM and add it to an FP32
-// accumulator in global memory with 16-byte vector reductions (red.global.add.v4.f32). dK and dV
-// stay in TMEM for the whole loop and are written once.
+// dQ_i is a partial sum over key tiles: the compute warps move it from TMEM through a swizzled
+// shared-memory staging tile and add it to an FP32 accumulator in global memory with TMA
+// reduce-add operations (cp.reduce.async.bulk.tensor, whole 128-byte lines) that run behind the
+// next tile's work. dK and dV stay in TMEM for the whole loop and are written once.
 //
-// Warps 0-3 compute, warp 4 is the TMA producer (no multicast), warp 5 issues the MMAs.
+// Warps 0-7 compute (warp w and w+4 share TMEM lane quadrant w%4 and split the 128 query columns of
+// the transposed tiles, 64 each), warp 8 is the TMA producer (no multicast), warp 9 issues the MMAs.
 // TMEM columns, D = 64:  S/P^T [0,128) dP^T [128,256) dV [256,320) dK [320,384) dQ [384,448)
 //               D = 128: S/P^T [0,128) dP^T and dQ share [128,256) dV [256,384) dK [384,512)
 // Every wait is bounded (tc_common.cuh).
 #include "kernels.cuh"
 #include "tc_common.cuh"
+
+#ifdef B200ATTN_TRACE
+// Debug builds only: clock64() stamps of the first CTA's MMA warp and compute thread 0, read back by
+// b200attn_debug_read_bwd_trace(). Slot = role * 2048 + iteration * 16 + point.
+__device__ long long g_bwd_trace[4096];
+#define BWD_TRACE(role, it, point)                                                              \
+    do {                                                                                        \
+        if (blockIdx.x == 0 && (it) < 128) g_bwd_trace[(role) * 2048 + (it) * 16 + (point)] = clock64(); \
+    } while (0)
+extern "C" int b200attn_debug_read_bwd_trace(long long* host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(long long) * (size_t)count);
+}
+#else
+#define BWD_TRACE(role, it, point) \
+    do {                           \
+    } while (0)
+#endif
 
 namespace b200attn {
 namespace {
@@ -33,8 +53,10 @@ namespace {
 constexpr int kBQ = 128;               // query rows per inner tile
 constexpr int kBKV = 128;              // key/value rows per CTA
 constexpr int kAtomBytes = 128 * 128;  // 128 rows x 64 bf16, 128-byte swizzled
-constexpr int kComputeThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kComputeThreads = 256;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 
 template <int D>
@@ -43,8 +65,13 @@ struct BwdCfg {
     static constexpr int kTileBytes = kAtoms * kAtomBytes;
     static constexpr int kQStages = 2;
     static constexpr int kDoStages = (D == 64) ? 2 : 1;
-    static constexpr int kDsBytes = 2 * kAtomBytes;  // 128 key rows x 128 queries, bf16
-    static constexpr int kSmemBytes = kTileBytes * (2 + kQStages + kDoStages) + kDsBytes + 1024;
+    static constexpr int kDsBytes = 2 * kAtomBytes;      // 128 key rows x 128 queries, bf16
+    static constexpr int kDqStageBytes = 2 * kAtomBytes;  // two 128 x 32 FP32 blocks of a dQ partial
+    static constexpr int kStatBytes = 2 * 2 * kBQ * 4;    // lse2 and D of a query tile, double-buffered
+    // The dynamic buffer is declared 1024-byte aligned, so no slack is added (at d = 128 the kernel
+    // uses all of the 227 KB a CTA can have).
+    static constexpr int kSmemBytes = kTileBytes * (2 + kQStages + kDoStages) + kDsBytes + kDqStageBytes + kStatBytes;
+    static constexpr int kDqRounds = D / 64;  // 32-column blocks per thread in a dQ partial
     static constexpr bool kDqAliased = (D == 128);
     static constexpr uint32_t kTmemCols = 512;
     static constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
@@ -60,17 +87,17 @@ struct BwdBarriers {
 template <int D, bool GRADS_F32>
 __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_constant__ TcBwdArgs a) {
     using Cfg = BwdCfg<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sK = smem;
     uint8_t* sV = sK + Cfg::kTileBytes;
     uint8_t* sQ = sV + Cfg::kTileBytes;
     uint8_t* sDO = sQ + Cfg::kQStages * Cfg::kTileBytes;
     uint8_t* sDS = sDO + Cfg::kDoStages * Cfg::kTileBytes;
+    uint8_t* sDQ = sDS + Cfg::kDsBytes;  // staging of dQ partials for the TMA reduce-add
+    float (*s_lse)[kBQ] = reinterpret_cast<float (*)[kBQ]>(sDQ + Cfg::kDqStageBytes);
+    float (*s_D)[kBQ] = s_lse + 2;
 
     __shared__ BwdBarriers bars;
-    __shared__ __align__(16) float s_lse[2][kBQ];
-    __shared__ __align__(16) float s_D[2][kBQ];
     __shared__ uint32_t tmem_base_slot;
     __shared__ uint32_t abort_flag;
 
@@ -99,9 +126,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
         mbar_init(&bars.dq_full, 1);
         mbar_init(&bars.dq_empty, kComputeThreads);
         abort_flag = 0;
+        if ((smem_u32(smem) & 1023u) != 0 && a.fault_word) atomicCAS(a.fault_word, 0u, kFaultWaitTimeout | 0xA11u);
         mbar_fence_init();
     }
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         tmem_alloc(&tmem_base_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -110,7 +138,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             tma_prefetch_desc(&a.map_q);
@@ -140,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             }
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_st = make_idesc_bf16(kBKV, kBQ, 0, 0);  // S^T, dP^T
         constexpr uint32_t idesc_kv = make_idesc_bf16(kBKV, D, 0, 1);    // dV, dK: B is MN-major
@@ -194,18 +222,24 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             // dV += P^T dO
             mbar_wait(&bars.p_ready, it & 1, &abort_flag, a.fault_word, 0x55);
             tc_fence_after();
+            if (lane == 0) BWD_TRACE(0, it, 0);
             if (lane == 0) {
                 const uint64_t do_mnmaj = make_smem_desc_sw128(smem_u32(sDO + os * Cfg::kTileBytes), kAtomBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)
-                    tc_mma_ts(tmem + Cfg::kColDV, tmem + Cfg::kColS + kk * 8, desc_advance(do_mnmaj, kk * 2048), idesc_kv,
-                              (it > 0) || (kk > 0));
+                    tc_mma_ts(tmem + Cfg::kColDV, tmem + Cfg::kColS + (kk >> 2) * 64 + (kk & 3) * 8,
+                              desc_advance(do_mnmaj, kk * 2048), idesc_kv, (it > 0) || (kk > 0));
                 tc_commit(&bars.do_empty[os]);  // dP^T(it) and dV(it) were the readers of this dO tile
             }
             __syncwarp();
+            if (lane == 0) BWD_TRACE(0, it, 1);
             if (it + 1 < n_it) issue_st(it + 1);  // overlaps the exponentials of the next tile with dK/dQ of this one
+            if (lane == 0) BWD_TRACE(0, it, 2);
             // dK += dS^T Q ; dQ = dS K
             mbar_wait(&bars.ds_ready, it & 1, &abort_flag, a.fault_word, 0x56);
+            if (lane == 0) BWD_TRACE(0, it, 3);
+            // dS^T(it) done means dP^T(it) has been consumed: with dQ in its own columns the next dP^T can go first
+            if (!Cfg::kDqAliased && it + 1 < n_it) issue_dp(it + 1);
             if (!Cfg::kDqAliased && it > 0)  // previous dQ partial must have been read out of its columns
                 mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x57);
             tc_fence_after();
@@ -225,53 +259,86 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 tc_commit(&bars.dq_full);
             }
             __syncwarp();
-            if (it + 1 < n_it) issue_dp(it + 1);
+            if (lane == 0) BWD_TRACE(0, it, 4);
+            if (Cfg::kDqAliased && it + 1 < n_it) issue_dp(it + 1);
+            if (lane == 0) BWD_TRACE(0, it, 5);
         }
     } else {
-        // ------------------------------------------------------------ compute warps: thread r = key row r
-        const int r = tid;
-        const uint32_t lane_base = uint32_t(warp) * 32u;
+        // ------------------------------------------------------------ compute warps: thread (r, half) =
+        // key row r (TMEM lane r), query columns [64*half, 64*half + 64) of the transposed tiles
+        const int r = tid & 127;
+        const int half = tid >> 7;
+        const int c_begin = half * (kBQ / 2);
+        const uint32_t lane_base = uint32_t(warp & 3) * 32u;
         const float scale_log2 = a.scale * kLog2e;
         const long long stat_base = (long long)bh * a.T;
 
-        auto drain_dq = [&](int it) {  // add the dQ partial of query tile jt+it to the FP32 accumulator
+        // A dQ partial (query tile jt+it) travels TMEM -> registers -> a 128-byte-swizzled staging
+        // tile -> TMA reduce-add into the FP32 accumulator in global memory (whole 128-byte lines
+        // instead of scattered atomics). Here thread (r, half) owns QUERY row r and the head-dim
+        // columns of its half; `dqv` holds them between the two steps below.
+        // One SM sustains only about 16 bytes/clock of FP32 reductions, so the reduce runs
+        // asynchronously behind the next tile's work and is waited for only when the staging tile is
+        // needed again; at d = 128 the partial is sent in two rounds of 32 columns per thread.
+        uint32_t dqv[D / 2];
+        auto dq_fetch = [&](int it) {  // TMEM -> registers; frees the dQ columns for the MMA warp
             mbar_wait(&bars.dq_full, it & 1, &abort_flag, a.fault_word, 0x60);
             tc_fence_after();
-            const int q_g = (jt + it) * kBQ + r;  // here thread r owns QUERY row r of the dQ tile
-            float* dst = a.dq_acc + (stat_base + q_g) * D;
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDQ + c), v);
-                tmem_wait_ld();
-                if (q_g < a.T) {
-#pragma unroll
-                    for (int x = 0; x < 32; x += 4)
-                        red_add_v4(dst + c + x, __uint_as_float(v[x]), __uint_as_float(v[x + 1]), __uint_as_float(v[x + 2]),
-                                   __uint_as_float(v[x + 3]));
-                }
-            }
+            for (int c = 0; c < D / 2; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDQ + half * (D / 2) + c), &dqv[c]);
+            tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&bars.dq_empty);
         };
+        auto dq_send = [&](int it, int rd) {  // registers -> staging -> reduce-add, 32 columns per thread
+            if (tid == 0) tma_store_wait_read();  // earlier reductions have finished reading the staging tile
+            named_bar_sync(2, kComputeThreads);
+            uint8_t* stage = sDQ + half * kAtomBytes;
+#pragma unroll
+            for (int x = 0; x < 32; x += 4)
+                *reinterpret_cast<uint4*>(stage + swz128(r, x >> 2)) =
+                    make_uint4(dqv[rd * 32 + x], dqv[rd * 32 + x + 1], dqv[rd * 32 + x + 2], dqv[rd * 32 + x + 3]);
+            fence_proxy_async_smem();
+            named_bar_sync(2, kComputeThreads);
+            if (tid == 0) {
+                tma_reduce_add_3d(&a.map_dq_acc, sDQ, rd * 32, (jt + it) * kBQ, bh);
+                tma_reduce_add_3d(&a.map_dq_acc, sDQ + kAtomBytes, D / 2 + rd * 32, (jt + it) * kBQ, bh);
+                tma_store_commit();
+            }
+        };
+
+        // statistics of the first query tile; later tiles are fetched one iteration ahead
+        float stat_next;
+        {
+            const int q_g = jt * kBQ + r;
+            stat_next = (half == 0) ? ((q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY)
+                                    : ((q_g < a.T) ? a.D[stat_base + q_g] : 0.f);
+        }
 
         for (int it = 0; it < n_it; ++it) {
             const int i = jt + it;
             const int buf = it & 1;
+            if (tid == 0) BWD_TRACE(1, it, 0);
             {   // per-query statistics of this tile: column c of the transposed tiles is query i*128 + c
-                const int q_g = i * kBQ + r;
-                s_lse[buf][r] = (q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY;  // +inf -> P = 0
-                s_D[buf][r] = (q_g < a.T) ? a.D[stat_base + q_g] : 0.f;
+                if (half == 0) s_lse[buf][r] = stat_next;  // +inf for queries beyond T -> P = 0
+                else s_D[buf][r] = stat_next;
+                const int q_g = (i + 1) * kBQ + r;  // prefetch for the next tile
+                if (it + 1 < n_it)
+                    stat_next = (half == 0) ? ((q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY)
+                                            : ((q_g < a.T) ? a.D[stat_base + q_g] : 0.f);
             }
             named_bar_sync(1, kComputeThreads);
 
             // ---- P^T
+            if (tid == 0) BWD_TRACE(1, it, 1);
             mbar_wait(&bars.s_full, it & 1, &abort_flag, a.fault_word, 0x61);
             tc_fence_after();
-            float p[kBQ];
+            if (tid == 0) BWD_TRACE(1, it, 2);
+            float p[kBQ / 2];
             const bool diag = (i == jt);
 #pragma unroll
-            for (int c = 0; c < kBQ; c += 32) {
+            for (int cc = 0; cc < kBQ / 2; cc += 32) {
+                const int c = c_begin + cc;
                 uint32_t sv[32];
                 tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColS + c), sv);
                 tmem_wait_ld();
@@ -284,25 +351,34 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     for (int y = 0; y < 4; ++y) {
                         float e = fast_exp2(fmaf(__uint_as_float(sv[x + y]), scale_log2, -l4[y]));
                         if (diag && (c + x + y) < r) e = 0.f;  // query before this key: masked
-                        p[c + x + y] = e;
+                        p[cc + x + y] = e;
                     }
-                    pk[x >> 1] = pack_bf16x2(p[c + x], p[c + x + 1]);
-                    pk[(x >> 1) + 1] = pack_bf16x2(p[c + x + 2], p[c + x + 3]);
+                    pk[x >> 1] = pack_bf16x2(p[cc + x], p[cc + x + 1]);
+                    pk[(x >> 1) + 1] = pack_bf16x2(p[cc + x + 2], p[cc + x + 3]);
                 }
-                tmem_st16(tmem_addr(tmem, lane_base, Cfg::kColS + (c >> 1)), pk);
+                // each half packs its P^T into the first 32 columns of its OWN 64 score columns, so the
+                // other half's unread scores are never overwritten
+                tmem_st16(tmem_addr(tmem, lane_base, Cfg::kColS + c_begin + (cc >> 1)), pk);
             }
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars.p_ready);
+            if (tid == 0) BWD_TRACE(1, it, 3);
 
             // ---- previous tile's dQ partial (its MMA ran while the exponentials above were computed)
-            if (it > 0) drain_dq(it - 1);
+            if (it > 0) {
+                dq_fetch(it - 1);
+                dq_send(it - 1, 0);
+            }
+            if (tid == 0) BWD_TRACE(1, it, 4);
 
             // ---- dS^T
             mbar_wait(&bars.dp_full, it & 1, &abort_flag, a.fault_word, 0x62);
             tc_fence_after();
+            if (tid == 0) BWD_TRACE(1, it, 5);
 #pragma unroll
-            for (int c = 0; c < kBQ; c += 32) {
+            for (int cc = 0; cc < kBQ / 2; cc += 32) {
+                const int c = c_begin + cc;
                 uint32_t dv[32];
                 tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDP + c), dv);
                 tmem_wait_ld();
@@ -313,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     const float dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
                     float ds[8];
 #pragma unroll
-                    for (int y = 0; y < 8; ++y) ds[y] = p[c + x + y] * (__uint_as_float(dv[x + y]) - dd[y]) * a.scale;
+                    for (int y = 0; y < 8; ++y) ds[y] = p[cc + x + y] * (__uint_as_float(dv[x + y]) - dd[y]) * a.scale;
                     uint4 w;
                     w.x = pack_bf16x2(ds[0], ds[1]);
                     w.y = pack_bf16x2(ds[2], ds[3]);
@@ -326,8 +402,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(&bars.ds_ready);
+            if (tid == 0) BWD_TRACE(1, it, 6);
+            if (Cfg::kDqRounds == 2 && it > 0) dq_send(it - 1, 1);  // second half of the previous partial
         }
-        drain_dq(n_it - 1);  // dq_full of the last tile also means every dV / dK MMA has retired
+        dq_fetch(n_it - 1);  // dq_full of the last tile also means every dV / dK MMA has retired
+        dq_send(n_it - 1, 0);
+        if (Cfg::kDqRounds == 2) dq_send(n_it - 1, 1);
+        if (tid == 0) tma_store_wait_all();
 
         // ---- epilogue: dV and dK of this key tile
         const int kv_g = jt * kBKV + r;
@@ -337,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             void* gout = which == 0 ? a.dv : a.dk;
             uint8_t* stage = sQ + which * Cfg::kTileBytes;  // Q stages are idle now
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
+            for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_addr(tmem, lane_base, col0 + c), v);
                 tmem_wait_ld();
@@ -379,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem, Cfg::kTmemCols);
+    if (warp == kProducerWarp) tmem_dealloc(tmem, Cfg::kTmemCols);
 }
 
 // ------------------------------------------------------------------ pre-pass
@@ -391,29 +472,37 @@ __device__ __forceinline__ float warp_sum(float x) {
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 
-// One warp per row: D[row] = sum_e dO*O (16-byte loads), lse2[row] = log-sum-exp in log2 units.
+// D[row] = sum_e dO*O and lse2[row] = log-sum-exp in log2 units. A row is shared by d/VEC adjacent
+// threads, 16 bytes (VEC elements) each, so a warp's loads are contiguous; the partial sums meet in a
+// sub-warp shuffle reduction. When `zero` is given, the same threads clear the FP32 dQ accumulator
+// row (4*d bytes) so that no separate memset pass is needed.
 template <typename TIn>
 __global__ void __launch_bounds__(256) bwd_prepass_kernel(const TIn* __restrict__ o, const TIn* __restrict__ dO,
                                                          const float* __restrict__ m, const float* __restrict__ l,
                                                          const float* __restrict__ lse, float* __restrict__ Dout,
-                                                         float* __restrict__ lse2, long long rows, int d) {
+                                                         float* __restrict__ lse2, float* __restrict__ zero,
+                                                         long long rows, int d) {
     constexpr int VEC = 16 / sizeof(TIn);
-    const int lane = threadIdx.x & 31;
-    long long row = blockIdx.x * 8ll + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const TIn* a = o + row * d;
-    const TIn* b = dO + row * d;
+    const int tpr = d / VEC;  // threads per row: a power of two <= 32
+    const long long gid = blockIdx.x * 256ll + threadIdx.x;
+    const long long row = gid / tpr;
+    const int e = int(gid % tpr) * VEC;
     float acc = 0.f;
-    for (int e = lane * VEC; e < d; e += 32 * VEC) {
-        uint4 ua = __ldg(reinterpret_cast<const uint4*>(a + e));
-        uint4 ub = __ldg(reinterpret_cast<const uint4*>(b + e));
+    if (row < rows) {
+        uint4 ua = __ldg(reinterpret_cast<const uint4*>(o + row * d + e));
+        uint4 ub = __ldg(reinterpret_cast<const uint4*>(dO + row * d + e));
         const TIn* pa = reinterpret_cast<const TIn*>(&ua);
         const TIn* pb = reinterpret_cast<const TIn*>(&ub);
 #pragma unroll
         for (int x = 0; x < VEC; ++x) acc = fmaf(to_f32(pa[x]), to_f32(pb[x]), acc);
+        if (zero) {
+            float4* z = reinterpret_cast<float4*>(zero + row * d + e);
+#pragma unroll
+            for (int x = 0; x < VEC / 4; ++x) z[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
+    for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (row < rows && e == 0) {
         Dout[row] = acc;
         if (lse2) lse2[row] = (lse ? lse[row] : (m[row] + logf(l[row]))) * kLog2e;
     }
@@ -442,17 +531,20 @@ cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream) {
 
 template <typename TIn>
 cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse, float* D,
-                               float* lse2, long long rows, int d, cudaStream_t stream) {
+                               float* lse2, float* zero, long long rows, int d, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
-    unsigned int blocks = (unsigned int)((rows + 7) / 8);
-    bwd_prepass_kernel<TIn><<<blocks, 256, 0, stream>>>(o, dO, m, l, lse, D, lse2, rows, d);
+    constexpr int VEC = 16 / sizeof(TIn);
+    const int tpr = d / VEC;
+    if (d % VEC != 0 || tpr > 32 || (tpr & (tpr - 1)) != 0) return cudaErrorInvalidValue;
+    const long long threads = rows * tpr;
+    bwd_prepass_kernel<TIn><<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(o, dO, m, l, lse, D, lse2, zero, rows, d);
     return cudaGetLastError();
 }
 template cudaError_t launch_bwd_prepass<float>(const float*, const float*, const float*, const float*, const float*,
-                                              float*, float*, long long, int, cudaStream_t);
+                                              float*, float*, float*, long long, int, cudaStream_t);
 template cudaError_t launch_bwd_prepass<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const float*,
-                                                      const float*, const float*, float*, float*, long long, int,
-                                                      cudaStream_t);
+                                                      const float*, const float*, float*, float*, float*, long long,
+                                                      int, cudaStream_t);
 
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {
     return launch_f32_to_bf16(dq_acc, dq, n, stream);

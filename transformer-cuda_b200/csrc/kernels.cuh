@@ -58,6 +58,7 @@ cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream);
 struct TcBwdArgs {
     CUtensorMap map_q, map_k, map_v, map_do;  // BF16 (d, T, BH)
     CUtensorMap map_dk, map_dv;               // BF16 outputs (used when grads_are_f32 == 0)
+    CUtensorMap map_dq_acc;                   // FP32 (d, T, BH) view of dq_acc, box 32 x 128 x 1, 128-byte swizzle
     const float* lse2;                        // (BH, T) log-sum-exp in log2 units: lse * log2(e)
     const float* D;                           // (BH, T) rowsum(dO * O)
     float* dq_acc;                            // (BH, T, d) FP32, zeroed before launch, receives sum of partials
@@ -71,10 +72,12 @@ struct TcBwdArgs {
 cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream);
 
 // Backward pre-pass: D = rowsum(dO*O) and lse2 = (m + log l) * log2(e) or lse * log2(e).
-// TIn is float or __nv_bfloat16. Exactly one of (m,l) / lse is given.
+// TIn is float or __nv_bfloat16. Exactly one of (m,l) / lse is given. If `zero` is not null the
+// pass also clears that (rows, d) FP32 buffer (the dQ accumulator). d/VEC (VEC = 16 bytes of TIn)
+// must be a power of two <= 32.
 template <typename TIn>
 cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse,
-                               float* D, float* lse2, long long rows, int d, cudaStream_t stream);
+                               float* D, float* lse2, float* zero, long long rows, int d, cudaStream_t stream);
 // dq (BF16) = dq_acc (FP32), elementwise.
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 

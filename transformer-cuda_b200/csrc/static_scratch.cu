@@ -96,12 +96,15 @@ int setup_current_device(PerDevice** out) {
     return B200ATTN_OK;
 }
 
-int encode_map(CUtensorMap* m, const void* base, int BH, int T, int d) {
+// BF16 tensors: 64 x 128 x 1 boxes; the FP32 dQ accumulator: 32 x 128 x 1 boxes (both 128 bytes per row).
+int encode_map(CUtensorMap* m, const void* base, int BH, int T, int d, bool f32 = false) {
+    const cuuint64_t esz = f32 ? 4 : 2;
     cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
-    cuuint64_t strides[2] = {cuuint64_t(d) * 2, cuuint64_t(T) * d * 2};
-    cuuint32_t box[3] = {64, 128, 1};
+    cuuint64_t strides[2] = {cuuint64_t(d) * esz, cuuint64_t(T) * d * esz};
+    cuuint32_t box[3] = {f32 ? 32u : 64u, 128, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode_fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = g_encode_fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                             const_cast<void*>(base), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", int(r));
@@ -152,6 +155,7 @@ extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const voi
     if ((rc = encode_map(&a.map_do, dO, BH, T, d))) return rc;
     if ((rc = encode_map(&a.map_dk, dk, BH, T, d))) return rc;
     if ((rc = encode_map(&a.map_dv, dv, BH, T, d))) return rc;
+    if ((rc = encode_map(&a.map_dq_acc, dq_acc, BH, T, d, true))) return rc;
     a.lse2 = lse2;
     a.D = D;
     a.dq_acc = dq_acc;
@@ -163,7 +167,7 @@ extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const voi
     a.fault_word = fault_word;
 
     cudaError_t e = launch_bwd_prepass<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dO),
-                                                      nullptr, nullptr, lse, D, lse2, (long long)rows, d, stream);
+                                                      nullptr, nullptr, lse, D, lse2, nullptr, (long long)rows, d, stream);
     if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "pre-pass launch: %s", cudaGetErrorString(e));
     // the accumulator still holds the previous call's sums: it must start from zero
     e = cudaMemsetAsync(dq_acc, 0, n * sizeof(float), stream);
