@@ -223,6 +223,7 @@ int run_fwd_tc(DeviceState* st, const void* q, const void* k, const void* v, voi
     a.l_out = l_out;
     a.lse_out = lse_out;
     a.BH = BH, a.T = T, a.d = d;
+    a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = st->fault_word;
     ScopedKernelTimer timer(0, stream);
@@ -252,6 +253,7 @@ int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, con
     a.dv = dv;
     a.grads_are_f32 = grads_f32 ? 1 : 0;
     a.BH = BH, a.T = T, a.d = d;
+    a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = st->fault_word;
     ScopedKernelTimer timer(1, stream);

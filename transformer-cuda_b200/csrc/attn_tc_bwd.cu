@@ -41,8 +41,25 @@ __device__ long long g_bwd_trace[4096];
 extern "C" int b200attn_debug_read_bwd_trace(long long* host, int count) {
     return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(long long) * (size_t)count);
 }
+// Per-CTA life line: {globaltimer at start, after prologue (first S^T ready), at loop end, at exit, smid, iterations}.
+__device__ long long g_bwd_cta_trace[8 * 4096];
+extern "C" int b200attn_debug_read_bwd_cta_trace(long long* host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, g_bwd_cta_trace, sizeof(long long) * (size_t)count);
+}
+__device__ __forceinline__ long long b200attn_globaltimer() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define BWD_CTA_TRACE(slot, value)                                                            \
+    do {                                                                                      \
+        if (blockIdx.x < 4096) g_bwd_cta_trace[blockIdx.x * 8 + (slot)] = (value);            \
+    } while (0)
 #else
 #define BWD_TRACE(role, it, point) \
+    do {                           \
+    } while (0)
+#define BWD_CTA_TRACE(slot, value) \
     do {                           \
     } while (0)
 #endif
@@ -106,9 +123,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     const int lane = tid & 31;
 
     const int n_tiles = (a.T + kBKV - 1) / kBKV;
-    const int bh = blockIdx.x / n_tiles;
-    const int jt = blockIdx.x % n_tiles;  // key tile; tile 0 sees every query tile and goes first
+    // CTA order. Key tile 0 sees every query tile and is the longest. When the whole problem fits in
+    // L2 the CTAs are issued longest-first across ALL slabs (shortest tail); otherwise slab by slab,
+    // so that the CTAs resident at one time share few slabs and their tiles stay in L2.
+    const int bh = a.tile_major_order ? int(blockIdx.x % a.BH) : int(blockIdx.x / n_tiles);
+    const int jt = a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_tiles);
     const int n_it = n_tiles - jt;        // query tiles jt .. n_tiles-1
+#ifdef B200ATTN_TRACE
+    if (threadIdx.x == 0) {
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        BWD_CTA_TRACE(0, b200attn_globaltimer());
+        BWD_CTA_TRACE(4, (long long)smid);
+        BWD_CTA_TRACE(5, (long long)n_it);
+    }
+#endif
 
     if (tid == 0) {
         mbar_init(&bars.k_full, 1);
@@ -334,6 +363,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             mbar_wait(&bars.s_full, it & 1, &abort_flag, a.fault_word, 0x61);
             tc_fence_after();
             if (tid == 0) BWD_TRACE(1, it, 2);
+#ifdef B200ATTN_TRACE
+            if (tid == 0 && it == 0) BWD_CTA_TRACE(1, b200attn_globaltimer());
+#endif
             float p[kBQ / 2];
             const bool diag = (i == jt);
 #pragma unroll
@@ -342,6 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 uint32_t sv[32];
                 tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColS + c), sv);
                 tmem_wait_ld();
+                if (tid == 0 && cc == 0) BWD_TRACE(1, it, 7);
                 uint32_t pk[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 4) {
@@ -358,9 +391,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 }
                 // each half packs its P^T into the first 32 columns of its OWN 64 score columns, so the
                 // other half's unread scores are never overwritten
+                if (tid == 0 && cc == 0) BWD_TRACE(1, it, 8);
                 tmem_st16(tmem_addr(tmem, lane_base, Cfg::kColS + c_begin + (cc >> 1)), pk);
             }
+            if (tid == 0) BWD_TRACE(1, it, 9);
             tmem_wait_st();
+            if (tid == 0) BWD_TRACE(1, it, 10);
             tc_fence_before();
             mbar_arrive(&bars.p_ready);
             if (tid == 0) BWD_TRACE(1, it, 3);
@@ -405,10 +441,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             if (tid == 0) BWD_TRACE(1, it, 6);
             if (Cfg::kDqRounds == 2 && it > 0) dq_send(it - 1, 1);  // second half of the previous partial
         }
+#ifdef B200ATTN_TRACE
+        if (tid == 0) BWD_CTA_TRACE(2, b200attn_globaltimer());
+#endif
         dq_fetch(n_it - 1);  // dq_full of the last tile also means every dV / dK MMA has retired
         dq_send(n_it - 1, 0);
         if (Cfg::kDqRounds == 2) dq_send(n_it - 1, 1);
-        if (tid == 0) tma_store_wait_all();
 
         // ---- epilogue: dV and dK of this key tile
         const int kv_g = jt * kBKV + r;
@@ -454,13 +492,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     tma_store_3d(&a.map_dk, sQ + Cfg::kTileBytes + at * kAtomBytes, at * 64, jt * kBKV, bh);
                 }
                 tma_store_commit();
-                tma_store_wait_all();
             }
         }
+        // shared memory must outlive the bulk reads of every store / reduce issued by this thread;
+        // their global writes complete before the grid does
+        if (tid == 0) tma_store_wait_read();
     }
     tc_fence_before();
     __syncthreads();
     if (warp == kProducerWarp) tmem_dealloc(tmem, Cfg::kTmemCols);
+#ifdef B200ATTN_TRACE
+    if (threadIdx.x == 0) BWD_CTA_TRACE(3, b200attn_globaltimer());
+#endif
 }
 
 // ------------------------------------------------------------------ pre-pass

@@ -10,15 +10,16 @@
 //              per thread, so row max / row sum need no cross-thread traffic), turned into
 //              P_j = exp2(S_j*scale*log2e - m) in BF16 and written back over S_j in TMEM, where the
 //              P.V MMA reads it as its A operand. The same threads rescale the O accumulator in
-//              TMEM when the running maximum moves, and run the epilogue.
+//              TMEM when the running maximum has moved by more than 2^8, and run the epilogue.
 //   warp 4     TMA producer: Q once, then a ring of K and V tiles (cp.async.bulk.tensor, 128-byte
 //              swizzle, no multicast), each signalled through an mbarrier with expect_tx.
-//   warp 5     MMA issuer: S_j = Q K_j^T (both operands K-major in shared memory) into one of two
-//              TMEM score buffers, and O += P_j V_j (A from TMEM, V as an MN-major shared-memory
-//              operand, so no transpose is materialised). QK^T of tile j+1 is issued before P.V of
-//              tile j so the tensor pipe works while the softmax warps are busy.
+//   warp 5     MMA issuer: S_j = Q K_j^T (both operands K-major in shared memory) into the TMEM
+//              score buffer, and O += P_j V_j (A from TMEM, V as an MN-major shared-memory
+//              operand, so no transpose is materialised).
 //
-// TMEM columns: [0,128) S/P buffer 0, [128,256) S/P buffer 1, [256,256+D) O.
+// A CTA uses 256 TMEM columns ([0,128) S/P, [128,128+D) O) and at most 96 KB of shared memory, so
+// two CTAs are resident per SM: while one CTA's softmax warps work on a tile, the other CTA's MMAs
+// and loads run, and the prologue / epilogue of one overlaps the main loop of the other.
 // Every mbarrier wait has an iteration limit (tc_common.cuh); a wait that gives up sets the fault
 // word and the kernel still runs to its end and frees its TMEM.
 #include "kernels.cuh"
@@ -39,24 +40,23 @@ template <int D>
 struct FwdCfg {
     static constexpr int kAtoms = D / 64;
     static constexpr int kTileBytes = kAtoms * kAtomBytes;
-    static constexpr int kStages = (D == 64) ? 3 : 2;
-    static constexpr int kSmemBytes = kTileBytes * (1 + 2 * kStages) + 1024;  // + alignment slack
-    static constexpr uint32_t kTmemCols = 512;
-    static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+    static constexpr int kStages = (D == 64) ? 2 : 1;
+    static constexpr int kSmemBytes = kTileBytes * (1 + 2 * kStages);  // dynamic buffer is declared 1024-aligned
+    static constexpr uint32_t kTmemCols = 256;
+    static constexpr uint32_t kColS = 0, kColO = 128;
 };
 
 struct FwdBarriers {
     uint64_t q_full;
     uint64_t k_full[3], v_full[3], k_empty[3], v_empty[3];
-    uint64_t s_full[2], p_full[2];
+    uint64_t s_full, p_full;
     uint64_t o_done;
 };
 
 template <int D, bool OUT_F32>
-__global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_constant__ TcFwdArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_constant__ TcFwdArgs a) {
     using Cfg = FwdCfg<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = smem + Cfg::kTileBytes;
     uint8_t* sV = sK + Cfg::kStages * Cfg::kTileBytes;
@@ -70,8 +70,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
     const int lane = tid & 31;
 
     const int n_q_tiles = (a.T + kBM - 1) / kBM;
-    const int bh = blockIdx.x / n_q_tiles;
-    const int qt = n_q_tiles - 1 - (blockIdx.x % n_q_tiles);  // long tiles first inside a slab
+    // CTA order: the last query tile of a slab is the longest. Longest-first across all slabs when the
+    // problem fits in L2 (shortest tail), else slab by slab (resident CTAs share K/V tiles in L2).
+    const int bh = a.tile_major_order ? int(blockIdx.x % a.BH) : int(blockIdx.x / n_q_tiles);
+    const int qt = n_q_tiles - 1 - (a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_q_tiles));
     const int n_kv = qt + 1;                                  // key tiles 0..qt; qt is the diagonal tile
 
     if (tid == 0) {
@@ -82,12 +84,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             mbar_init(&bars.k_empty[s], 1);
             mbar_init(&bars.v_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&bars.s_full[b], 1);
-            mbar_init(&bars.p_full[b], kSoftmaxThreads);
-        }
+        mbar_init(&bars.s_full, 1);
+        mbar_init(&bars.p_full, kSoftmaxThreads);
         mbar_init(&bars.o_done, 1);
         abort_flag = 0;
+        if ((smem_u32(smem) & 1023u) != 0 && a.fault_word) atomicCAS(a.fault_word, 0u, kFaultWaitTimeout | 0xA10u);
         mbar_fence_init();
     }
     if (warp == 4) {
@@ -128,56 +129,55 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
         constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, D, 0, 1);
         const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 0, 1024);
         mbar_wait(&bars.q_full, 0, &abort_flag, a.fault_word, 0x20);
-        for (int j = 0; j <= n_kv; ++j) {
-            if (j < n_kv) {
-                // S[j&1] = Q K_j^T
-                const int s = j % Cfg::kStages;
-                mbar_wait(&bars.k_full[s], (j / Cfg::kStages) & 1, &abort_flag, a.fault_word, 0x21);
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + s * Cfg::kTileBytes), 0, 1024);
-                    const uint32_t d_tmem = tmem + ((j & 1) ? Cfg::kColS1 : Cfg::kColS0);
+        for (int j = 0; j < n_kv; ++j) {
+            const int s = j % Cfg::kStages;
+            const uint32_t ring_phase = (j / Cfg::kStages) & 1;
+            // S = Q K_j^T (the score buffer is free: P_{j-1} V_{j-1} was issued before, and MMAs run in order)
+            mbar_wait(&bars.k_full[s], ring_phase, &abort_flag, a.fault_word, 0x21);
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + s * Cfg::kTileBytes), 0, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
-                        tc_mma_ss(d_tmem, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk, kk > 0);
-                    }
-                    tc_commit(&bars.k_empty[s]);
-                    tc_commit(&bars.s_full[j & 1]);
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
+                    tc_mma_ss(tmem + Cfg::kColS, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk, kk > 0);
                 }
-                __syncwarp();
+                tc_commit(&bars.k_empty[s]);
+                tc_commit(&bars.s_full);
             }
-            if (j >= 1) {
-                // O += P_{j-1} V_{j-1}
-                const int jp = j - 1;
-                const int s = jp % Cfg::kStages;
-                mbar_wait(&bars.v_full[s], (jp / Cfg::kStages) & 1, &abort_flag, a.fault_word, 0x22);
-                mbar_wait(&bars.p_full[jp & 1], (jp >> 1) & 1, &abort_flag, a.fault_word, 0x23);
-                tc_fence_after();
-                if (lane == 0) {
-                    // V tile: rows = key index (the MMA's K), 64-column atoms along the head dim (its N)
-                    const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + s * Cfg::kTileBytes), kAtomBytes, 1024);
-                    const uint32_t p_tmem = tmem + ((jp & 1) ? Cfg::kColS1 : Cfg::kColS0);
+            __syncwarp();
+            // O += P_j V_j
+            mbar_wait(&bars.v_full[s], ring_phase, &abort_flag, a.fault_word, 0x22);
+            mbar_wait(&bars.p_full, j & 1, &abort_flag, a.fault_word, 0x23);
+            tc_fence_after();
+            if (lane == 0) {
+                // V tile: rows = key index (the MMA's K), 64-column atoms along the head dim (its N)
+                const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + s * Cfg::kTileBytes), kAtomBytes, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk)
-                        tc_mma_ts(tmem + Cfg::kColO, p_tmem + kk * 8, desc_advance(v_desc, kk * 2048), idesc_pv,
-                                  (jp > 0) || (kk > 0));
-                    tc_commit(&bars.v_empty[s]);
-                    tc_commit(&bars.o_done);
-                }
-                __syncwarp();
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    tc_mma_ts(tmem + Cfg::kColO, tmem + Cfg::kColS + kk * 8, desc_advance(v_desc, kk * 2048), idesc_pv,
+                              (j > 0) || (kk > 0));
+                tc_commit(&bars.v_empty[s]);
+                tc_commit(&bars.o_done);
             }
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------ softmax + correction + epilogue
         const int r = tid;                                // query row inside the tile, TMEM lane
         const uint32_t lane_base = uint32_t(warp) * 32u;  // this warp's TMEM lane quadrant
         const float scale_log2 = a.scale * kLog2e;
-        float m_run = -INFINITY;  // running maximum of scale*log2e*s
+        // Exponents are taken relative to m_ref, which follows the true running maximum m_true only
+        // when that has moved by more than kRescaleThreshold (in log2 units): P stays below
+        // 2^threshold, and the O accumulator in TMEM has to be rescaled only on those rare moves.
+        constexpr float kRescaleThreshold = 8.0f;
+        float m_true = -INFINITY;  // running maximum of scale*log2e*s
+        float m_ref = -INFINITY;   // reference the exponentials and l_run are relative to
         float l_run = 0.f;
         for (int j = 0; j < n_kv; ++j) {
-            const uint32_t s_col = (j & 1) ? Cfg::kColS1 : Cfg::kColS0;
-            mbar_wait(&bars.s_full[j & 1], (j >> 1) & 1, &abort_flag, a.fault_word, 0x30);
+            constexpr uint32_t s_col = Cfg::kColS;
+            // s_full(j) also means P.V of tile j-1 has retired (MMAs run in order), so O is up to date
+            mbar_wait(&bars.s_full, j & 1, &abort_flag, a.fault_word, 0x30);
             tc_fence_after();
             uint32_t sv[kBN];
 #pragma unroll
@@ -191,40 +191,40 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            const float alpha = fast_exp2(m_run - m_new);  // 0 on the first tile
+            m_true = fmaxf(m_true, mx * scale_log2);
+            const bool move = (j == 0) || (m_true - m_ref > kRescaleThreshold);
+            float alpha = 1.0f;
+            if (move) {
+                alpha = fast_exp2(m_ref - m_true);  // 0 on the first tile
+                m_ref = m_true;
+            }
             float sum = 0.f;
             uint32_t pk[kBN / 2];
 #pragma unroll
             for (int c = 0; c < kBN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_new));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_new));
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_ref));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_ref));
                 sum += p0 + p1;
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }
             l_run = l_run * alpha + sum;
-            m_run = m_new;
 #pragma unroll
             for (int c = 0; c < kBN / 2; c += 32) tmem_st32(tmem_addr(tmem, lane_base, s_col + c), &pk[c]);
-            if (j > 0) {
-                // O holds the sum up to tile j-1 once P.V of tile j-1 has retired; bring it to the new maximum.
-                mbar_wait(&bars.o_done, (j - 1) & 1, &abort_flag, a.fault_word, 0x31);
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+            if (j > 0 && __any_sync(0xffffffffu, move)) {
+                // bring the O accumulator to the new reference (rows that did not move use alpha = 1)
 #pragma unroll
-                    for (int c = 0; c < D; c += 32) {
-                        uint32_t ov[32];
-                        tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColO + c), ov);
-                        tmem_wait_ld();
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColO + c), ov);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-                        tmem_st32(tmem_addr(tmem, lane_base, Cfg::kColO + c), ov);
-                    }
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                    tmem_st32(tmem_addr(tmem, lane_base, Cfg::kColO + c), ov);
                 }
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars.p_full[j & 1]);
+            mbar_arrive(&bars.p_full);
         }
         // ---- epilogue: O / l
         mbar_wait(&bars.o_done, (n_kv - 1) & 1, &abort_flag, a.fault_word, 0x32);
@@ -233,9 +233,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
         const int row_g = qt * kBM + r;
         const long long stat_idx = (long long)bh * a.T + row_g;
         if (row_g < a.T) {
-            if (a.m_out) a.m_out[stat_idx] = m_run * kLn2;
-            if (a.l_out) a.l_out[stat_idx] = l_run;
-            if (a.lse_out) a.lse_out[stat_idx] = (m_run + log2f(l_run)) * kLn2;
+            // exported statistics are relative to the true row maximum
+            if (a.m_out) a.m_out[stat_idx] = m_true * kLn2;
+            if (a.l_out) a.l_out[stat_idx] = l_run * exp2f(m_ref - m_true);
+            if (a.lse_out) a.lse_out[stat_idx] = (m_ref + log2f(l_run)) * kLn2;
         }
 #pragma unroll
         for (int c = 0; c < D; c += 32) {
@@ -271,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             if (tid == 0) {
                 for (int at = 0; at < Cfg::kAtoms; ++at) tma_store_3d(&a.map_o, sQ + at * kAtomBytes, at * 64, qt * kBM, bh);
                 tma_store_commit();
-                tma_store_wait_all();
+                tma_store_wait_read();  // the staging tile must outlive the bulk read; the write completes with the grid
             }
         }
     }

@@ -50,6 +50,7 @@ struct TcFwdArgs {
     float* l_out;                            // optional (BH, T): sum exp(s - m)
     float* lse_out;                          // optional (BH, T): m + log(l)
     int BH, T, d;
+    int tile_major_order;  // 1: CTAs ordered longest tile first across all slabs; 0: slab by slab
     float scale;
     unsigned int* fault_word;
 };
@@ -66,6 +67,7 @@ struct TcBwdArgs {
     void* dv;
     int grads_are_f32;
     int BH, T, d;
+    int tile_major_order;  // 1: CTAs ordered longest tile first across all slabs; 0: slab by slab
     float scale;
     unsigned int* fault_word;
 };

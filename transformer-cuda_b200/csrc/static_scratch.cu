@@ -163,6 +163,7 @@ extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const voi
     a.dv = dv;
     a.grads_are_f32 = 0;
     a.BH = BH, a.T = T, a.d = d;
+    a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = fault_word;
 
