@@ -4,26 +4,46 @@
 // + causal mask) V with the row maximum m and the un-normalised row sum l exported.
 //
 // One CTA owns one 128-row query tile of one (batch, head) slab and walks the key/value tiles
-// 0..diagonal (tiles above the diagonal are never loaded). Six warps, three roles:
+// 0..diagonal (tiles above the diagonal are never loaded). Ten warps, three roles:
 //
-//   warps 0-3  softmax: thread r owns query row r. S_j is read from TMEM with tcgen05.ld (one row
-//              per thread, so row max / row sum need no cross-thread traffic), turned into
-//              P_j = exp2(S_j*scale*log2e - m) in BF16 and written back over S_j in TMEM, where the
-//              P.V MMA reads it as its A operand. The same threads rescale the O accumulator in
-//              TMEM when the running maximum has moved by more than 2^8, and run the epilogue.
-//   warp 4     TMA producer: Q once, then a ring of K and V tiles (cp.async.bulk.tensor, 128-byte
+//   warps 0-7  softmax: query row r (TMEM lane r) is shared by two threads, (r, 0) in warps 0-3 and
+//              (r, 1) in warps 4-7, which take key columns [0,64) and [64,128) of the tile. S_j is
+//              read from TMEM with tcgen05.ld; the two halves of a row exchange their partial row
+//              maximum through shared memory, turn their columns into P_j = exp2(S_j*scale*log2e - m)
+//              in BF16 and write them back over their own S columns in TMEM, where the P.V MMA reads
+//              them as its A operand. Row sums stay per thread and meet in the epilogue. The same
+//              threads rescale the O accumulator in TMEM when the running maximum has moved by more
+//              than 2^8, and run the epilogue.
+//   warp 8     TMA producer: Q once, then a ring of K and V tiles (cp.async.bulk.tensor, 128-byte
 //              swizzle, no multicast), each signalled through an mbarrier with expect_tx.
-//   warp 5     MMA issuer: S_j = Q K_j^T (both operands K-major in shared memory) into the TMEM
-//              score buffer, and O += P_j V_j (A from TMEM, V as an MN-major shared-memory
-//              operand, so no transpose is materialised).
+//   warp 9     MMA issuer: S_j = Q K_j^T (both operands K-major in shared memory) into one of three
+//              TMEM score buffers, and O += P_j V_j (A from TMEM, V as an MN-major shared-memory
+//              operand, so no transpose is materialised). QK^T runs two tiles ahead of P.V: MMAs
+//              execute in issue order, so with only one tile of lead every QK^T would queue behind a
+//              P.V that is itself waiting for the softmax warps.
 //
-// A CTA uses 256 TMEM columns ([0,128) S/P, [128,128+D) O) and at most 96 KB of shared memory, so
-// two CTAs are resident per SM: while one CTA's softmax warps work on a tile, the other CTA's MMAs
-// and loads run, and the prologue / epilogue of one overlaps the main loop of the other.
+// TMEM columns: [0,128) [128,256) [256,384) S/P buffers 0-2, [384,384+D) O.
 // Every mbarrier wait has an iteration limit (tc_common.cuh); a wait that gives up sets the fault
 // word and the kernel still runs to its end and frees its TMEM.
 #include "kernels.cuh"
 #include "tc_common.cuh"
+
+#ifdef B200ATTN_TRACE
+// Debug builds only: clock64() stamps of the first CTA's MMA warp and softmax thread 0.
+// Slot = role * 2048 + tile * 16 + point.
+__device__ long long g_fwd_trace[4096];
+#define FWD_TRACE(role, j, point)                                                              \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && (j) < 128) g_fwd_trace[(role) * 2048 + (j) * 16 + (point)] = clock64(); \
+    } while (0)
+extern "C" int b200attn_debug_read_fwd_trace(long long* host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(long long) * (size_t)count);
+}
+#else
+#define FWD_TRACE(role, j, point) \
+    do {                          \
+    } while (0)
+#endif
 
 namespace b200attn {
 namespace {
@@ -31,8 +51,11 @@ namespace {
 constexpr int kBM = 128;                 // query rows per CTA
 constexpr int kBN = 128;                 // key/value rows per tile
 constexpr int kAtomBytes = 128 * 128;    // one TMA box: 128 rows x 64 bf16, 128-byte swizzled
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kHalfCols = kBN / 2;       // key columns per softmax thread
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -40,30 +63,33 @@ template <int D>
 struct FwdCfg {
     static constexpr int kAtoms = D / 64;
     static constexpr int kTileBytes = kAtoms * kAtomBytes;
-    static constexpr int kStages = (D == 64) ? 2 : 1;
-    static constexpr int kSmemBytes = kTileBytes * (1 + 2 * kStages);  // dynamic buffer is declared 1024-aligned
-    static constexpr uint32_t kTmemCols = 256;
-    static constexpr uint32_t kColS = 0, kColO = 128;
+    static constexpr int kKStages = 3;  // K is consumed two tiles ahead of V
+    static constexpr int kVStages = (D == 64) ? 4 : 3;
+    static constexpr int kSBuffers = 3;
+    static constexpr int kSmemBytes = kTileBytes * (1 + kKStages + kVStages);  // dynamic buffer is declared 1024-aligned
+    static constexpr uint32_t kTmemCols = 512;
+    static constexpr uint32_t kColS = 0, kColO = 384;  // score buffer b at columns 128*b
 };
 
 struct FwdBarriers {
     uint64_t q_full;
-    uint64_t k_full[3], v_full[3], k_empty[3], v_empty[3];
-    uint64_t s_full, p_full;
+    uint64_t k_full[4], v_full[4], k_empty[4], v_empty[4];
+    uint64_t s_full[3], p_full[3];
     uint64_t o_done;
 };
 
 template <int D, bool OUT_F32>
-__global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_constant__ TcFwdArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_constant__ TcFwdArgs a) {
     using Cfg = FwdCfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = smem + Cfg::kTileBytes;
-    uint8_t* sV = sK + Cfg::kStages * Cfg::kTileBytes;
+    uint8_t* sV = sK + Cfg::kKStages * Cfg::kTileBytes;
 
     __shared__ FwdBarriers bars;
     __shared__ uint32_t tmem_base_slot;
     __shared__ uint32_t abort_flag;
+    __shared__ float s_xchg[2][2][kBM];  // [tile parity][half][row]: partial row maxima, then row sums
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -78,20 +104,22 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_c
 
     if (tid == 0) {
         mbar_init(&bars.q_full, 1);
-        for (int s = 0; s < 3; ++s) {
+        for (int s = 0; s < 4; ++s) {
             mbar_init(&bars.k_full[s], 1);
             mbar_init(&bars.v_full[s], 1);
             mbar_init(&bars.k_empty[s], 1);
             mbar_init(&bars.v_empty[s], 1);
         }
-        mbar_init(&bars.s_full, 1);
-        mbar_init(&bars.p_full, kSoftmaxThreads);
+        for (int b = 0; b < 3; ++b) {
+            mbar_init(&bars.s_full[b], 1);
+            mbar_init(&bars.p_full[b], kSoftmaxThreads);
+        }
         mbar_init(&bars.o_done, 1);
         abort_flag = 0;
         if ((smem_u32(smem) & 1023u) != 0 && a.fault_word) atomicCAS(a.fault_word, 0u, kFaultWaitTimeout | 0xA10u);
         mbar_fence_init();
     }
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         tmem_alloc(&tmem_base_slot, Cfg::kTmemCols);
         tmem_relinquish();
     }
@@ -100,7 +128,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_c
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             tma_prefetch_desc(&a.map_q);
@@ -110,87 +138,111 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_c
             for (int at = 0; at < Cfg::kAtoms; ++at)
                 tma_load_3d(sQ + at * kAtomBytes, &a.map_q, &bars.q_full, at * 64, qt * kBM, bh);
             for (int j = 0; j < n_kv; ++j) {
-                const int s = j % Cfg::kStages;
-                const int round = j / Cfg::kStages;
-                if (round > 0) mbar_wait(&bars.k_empty[s], (round - 1) & 1, &abort_flag, a.fault_word, 0x10);
-                mbar_expect_tx(&bars.k_full[s], Cfg::kTileBytes);
+                const int ks = j % Cfg::kKStages, kround = j / Cfg::kKStages;
+                if (kround > 0) mbar_wait(&bars.k_empty[ks], (kround - 1) & 1, &abort_flag, a.fault_word, 0x10);
+                mbar_expect_tx(&bars.k_full[ks], Cfg::kTileBytes);
                 for (int at = 0; at < Cfg::kAtoms; ++at)
-                    tma_load_3d(sK + s * Cfg::kTileBytes + at * kAtomBytes, &a.map_k, &bars.k_full[s], at * 64, j * kBN, bh);
-                if (round > 0) mbar_wait(&bars.v_empty[s], (round - 1) & 1, &abort_flag, a.fault_word, 0x11);
-                mbar_expect_tx(&bars.v_full[s], Cfg::kTileBytes);
+                    tma_load_3d(sK + ks * Cfg::kTileBytes + at * kAtomBytes, &a.map_k, &bars.k_full[ks], at * 64, j * kBN, bh);
+                const int vs = j % Cfg::kVStages, vround = j / Cfg::kVStages;
+                if (vround > 0) mbar_wait(&bars.v_empty[vs], (vround - 1) & 1, &abort_flag, a.fault_word, 0x11);
+                mbar_expect_tx(&bars.v_full[vs], Cfg::kTileBytes);
                 for (int at = 0; at < Cfg::kAtoms; ++at)
-                    tma_load_3d(sV + s * Cfg::kTileBytes + at * kAtomBytes, &a.map_v, &bars.v_full[s], at * 64, j * kBN, bh);
+                    tma_load_3d(sV + vs * Cfg::kTileBytes + at * kAtomBytes, &a.map_v, &bars.v_full[vs], at * 64, j * kBN, bh);
             }
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = make_idesc_bf16(kBM, kBN, 0, 0);
         constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, D, 0, 1);
         const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 0, 1024);
         mbar_wait(&bars.q_full, 0, &abort_flag, a.fault_word, 0x20);
-        for (int j = 0; j < n_kv; ++j) {
-            const int s = j % Cfg::kStages;
-            const uint32_t ring_phase = (j / Cfg::kStages) & 1;
-            // S = Q K_j^T (the score buffer is free: P_{j-1} V_{j-1} was issued before, and MMAs run in order)
-            mbar_wait(&bars.k_full[s], ring_phase, &abort_flag, a.fault_word, 0x21);
+        // S[j % 3] = Q K_j^T. The buffer is free: P_{j-3} V_{j-3} was issued before, and MMAs run in order.
+        auto issue_qk = [&](int j) {
+            const int ks = j % Cfg::kKStages;
+            mbar_wait(&bars.k_full[ks], (j / Cfg::kKStages) & 1, &abort_flag, a.fault_word, 0x21);
             tc_fence_after();
+            if (lane == 0) FWD_TRACE(0, j, 0);
             if (lane == 0) {
-                const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + s * Cfg::kTileBytes), 0, 1024);
+                const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + ks * Cfg::kTileBytes), 0, 1024);
+                const uint32_t d_tmem = tmem + Cfg::kColS + (j % Cfg::kSBuffers) * 128;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
-                    tc_mma_ss(tmem + Cfg::kColS, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk, kk > 0);
+                    tc_mma_ss(d_tmem, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk, kk > 0);
                 }
-                tc_commit(&bars.k_empty[s]);
-                tc_commit(&bars.s_full);
+                tc_commit(&bars.k_empty[ks]);
+                tc_commit(&bars.s_full[j % Cfg::kSBuffers]);
             }
             __syncwarp();
+            if (lane == 0) FWD_TRACE(0, j, 1);
+        };
+        issue_qk(0);
+        if (n_kv > 1) issue_qk(1);
+        for (int j = 0; j < n_kv; ++j) {
+            if (j + 2 < n_kv) issue_qk(j + 2);  // does not depend on the softmax of tile j
             // O += P_j V_j
-            mbar_wait(&bars.v_full[s], ring_phase, &abort_flag, a.fault_word, 0x22);
-            mbar_wait(&bars.p_full, j & 1, &abort_flag, a.fault_word, 0x23);
+            const int vs = j % Cfg::kVStages;
+            const int b = j % Cfg::kSBuffers;
+            mbar_wait(&bars.v_full[vs], (j / Cfg::kVStages) & 1, &abort_flag, a.fault_word, 0x22);
+            mbar_wait(&bars.p_full[b], (j / Cfg::kSBuffers) & 1, &abort_flag, a.fault_word, 0x23);
             tc_fence_after();
+            if (lane == 0) FWD_TRACE(0, j, 2);
             if (lane == 0) {
                 // V tile: rows = key index (the MMA's K), 64-column atoms along the head dim (its N)
-                const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + s * Cfg::kTileBytes), kAtomBytes, 1024);
+                const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + vs * Cfg::kTileBytes), kAtomBytes, 1024);
+                const uint32_t p_tmem = tmem + Cfg::kColS + b * 128;
+                // keys 0-63 of the tile are packed in columns [0,32) of the buffer, keys 64-127 in [64,96)
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    tc_mma_ts(tmem + Cfg::kColO, tmem + Cfg::kColS + kk * 8, desc_advance(v_desc, kk * 2048), idesc_pv,
-                              (j > 0) || (kk > 0));
-                tc_commit(&bars.v_empty[s]);
+                    tc_mma_ts(tmem + Cfg::kColO, p_tmem + (kk >> 2) * kHalfCols + (kk & 3) * 8,
+                              desc_advance(v_desc, kk * 2048), idesc_pv, (j > 0) || (kk > 0));
+                tc_commit(&bars.v_empty[vs]);
                 tc_commit(&bars.o_done);
             }
             __syncwarp();
+            if (lane == 0) FWD_TRACE(0, j, 3);
         }
     } else {
         // ------------------------------------------------------------ softmax + correction + epilogue
-        const int r = tid;                                // query row inside the tile, TMEM lane
-        const uint32_t lane_base = uint32_t(warp) * 32u;  // this warp's TMEM lane quadrant
+        const int r = tid & 127;                              // query row inside the tile, TMEM lane
+        const int half = tid >> 7;                            // which 64 key columns of a tile
+        const uint32_t lane_base = uint32_t(warp & 3) * 32u;  // this warp's TMEM lane quadrant
+        const int c_begin = half * kHalfCols;
         const float scale_log2 = a.scale * kLog2e;
         // Exponents are taken relative to m_ref, which follows the true running maximum m_true only
         // when that has moved by more than kRescaleThreshold (in log2 units): P stays below
         // 2^threshold, and the O accumulator in TMEM has to be rescaled only on those rare moves.
+        // Both threads of a row see the same maxima and so take the same decisions.
         constexpr float kRescaleThreshold = 8.0f;
-        float m_true = -INFINITY;  // running maximum of scale*log2e*s
+        float m_true = -INFINITY;  // running maximum of scale*log2e*s over the whole row
         float m_ref = -INFINITY;   // reference the exponentials and l_run are relative to
-        float l_run = 0.f;
+        float l_run = 0.f;         // this thread's share of the row sum
         for (int j = 0; j < n_kv; ++j) {
-            constexpr uint32_t s_col = Cfg::kColS;
-            // s_full(j) also means P.V of tile j-1 has retired (MMAs run in order), so O is up to date
-            mbar_wait(&bars.s_full, j & 1, &abort_flag, a.fault_word, 0x30);
+            const int sb = j % Cfg::kSBuffers;
+            const uint32_t s_col = Cfg::kColS + sb * 128 + c_begin;
+            if (tid == 0) FWD_TRACE(1, j, 0);
+            mbar_wait(&bars.s_full[sb], (j / Cfg::kSBuffers) & 1, &abort_flag, a.fault_word, 0x30);
             tc_fence_after();
-            uint32_t sv[kBN];
+            if (tid == 0) FWD_TRACE(1, j, 1);
+            uint32_t sv[kHalfCols];
 #pragma unroll
-            for (int c = 0; c < kBN; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, s_col + c), &sv[c]);
+            for (int c = 0; c < kHalfCols; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, s_col + c), &sv[c]);
             tmem_wait_ld();
+            if (tid == 0) FWD_TRACE(1, j, 2);
             if (j == qt) {  // diagonal tile: key c is visible to query r iff c <= r
 #pragma unroll
-                for (int c = 0; c < kBN; ++c)
-                    if (c > r) sv[c] = 0xff800000u;  // -inf
+                for (int c = 0; c < kHalfCols; ++c)
+                    if (c_begin + c > r) sv[c] = 0xff800000u;  // -inf
             }
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+            for (int c = 0; c < kHalfCols; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+            // row maximum over both halves (the buffer alternates with the tile parity, so one barrier per tile is enough)
+            s_xchg[j & 1][half][r] = mx;
+            named_bar_sync(1, kSoftmaxThreads);
+            mx = fmaxf(mx, s_xchg[j & 1][half ^ 1][r]);
+            if (tid == 0) FWD_TRACE(1, j, 3);
             m_true = fmaxf(m_true, mx * scale_log2);
             const bool move = (j == 0) || (m_true - m_ref > kRescaleThreshold);
             float alpha = 1.0f;
@@ -199,21 +251,25 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_c
                 m_ref = m_true;
             }
             float sum = 0.f;
-            uint32_t pk[kBN / 2];
+            uint32_t pk[kHalfCols / 2];
 #pragma unroll
-            for (int c = 0; c < kBN; c += 2) {
+            for (int c = 0; c < kHalfCols; c += 2) {
                 const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_ref));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_ref));
                 sum += p0 + p1;
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }
             l_run = l_run * alpha + sum;
-#pragma unroll
-            for (int c = 0; c < kBN / 2; c += 32) tmem_st32(tmem_addr(tmem, lane_base, s_col + c), &pk[c]);
+            if (tid == 0) FWD_TRACE(1, j, 4);
+            // each half packs its P into the first 32 columns of its OWN 64 score columns
+            tmem_st32(tmem_addr(tmem, lane_base, s_col), pk);
             if (j > 0 && __any_sync(0xffffffffu, move)) {
-                // bring the O accumulator to the new reference (rows that did not move use alpha = 1)
+                // bring this thread's half of the O accumulator to the new reference (rows that did not move
+                // use alpha = 1); O is complete up to tile j-1 once its P.V has retired
+                mbar_wait(&bars.o_done, (j - 1) & 1, &abort_flag, a.fault_word, 0x31);
+                tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < D; c += 32) {
+                for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
                     uint32_t ov[32];
                     tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColO + c), ov);
                     tmem_wait_ld();
@@ -224,22 +280,27 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_c
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars.p_full);
+            mbar_arrive(&bars.p_full[sb]);
+            if (tid == 0) FWD_TRACE(1, j, 5);
         }
         // ---- epilogue: O / l
+        // the two halves of a row add up their sums (buffer parity n_kv & 1 was last used two tiles ago)
+        s_xchg[n_kv & 1][half][r] = l_run;
+        named_bar_sync(1, kSoftmaxThreads);
+        l_run += s_xchg[n_kv & 1][half ^ 1][r];
         mbar_wait(&bars.o_done, (n_kv - 1) & 1, &abort_flag, a.fault_word, 0x32);
         tc_fence_after();
         const float inv_l = 1.0f / l_run;
         const int row_g = qt * kBM + r;
         const long long stat_idx = (long long)bh * a.T + row_g;
-        if (row_g < a.T) {
+        if (row_g < a.T && half == 0) {
             // exported statistics are relative to the true row maximum
             if (a.m_out) a.m_out[stat_idx] = m_true * kLn2;
             if (a.l_out) a.l_out[stat_idx] = l_run * exp2f(m_ref - m_true);
             if (a.lse_out) a.lse_out[stat_idx] = (m_ref + log2f(l_run)) * kLn2;
         }
 #pragma unroll
-        for (int c = 0; c < D; c += 32) {
+        for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
             uint32_t ov[32];
             tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColO + c), ov);
             tmem_wait_ld();
@@ -278,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_kernel(const __grid_c
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem, Cfg::kTmemCols);
+    if (warp == kProducerWarp) tmem_dealloc(tmem, Cfg::kTmemCols);
 }
 
 template <int D, bool OUT_F32>
@@ -297,6 +358,8 @@ cudaError_t launch_fwd(const TcFwdArgs& a, cudaStream_t stream) {
 
 cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream) {
     if (a.BH == 0 || a.T == 0) return cudaSuccess;
+    // Few key tiles per CTA: the two-CTAs-per-SM variant hides the per-CTA prologue and epilogue better.
+    if (a.T <= 2048) return launch_attn_fwd_tc_short(a, stream);
     if (a.d == 64) return a.out_is_f32 ? launch_fwd<64, true>(a, stream) : launch_fwd<64, false>(a, stream);
     if (a.d == 128) return a.out_is_f32 ? launch_fwd<128, true>(a, stream) : launch_fwd<128, false>(a, stream);
     return cudaErrorInvalidValue;

@@ -54,7 +54,8 @@ struct TcFwdArgs {
     float scale;
     unsigned int* fault_word;
 };
-cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream);
+cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream);        // picks the variant by T
+cudaError_t launch_attn_fwd_tc_short(const TcFwdArgs& a, cudaStream_t stream);  // two CTAs per SM, T <= 2048
 
 struct TcBwdArgs {
     CUtensorMap map_q, map_k, map_v, map_do;  // BF16 (d, T, BH)
