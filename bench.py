@@ -165,6 +165,91 @@ def run_reference(args, B, H, T, d):
     }), flush=True)
 
 
+def run_path_kernels(args, B, H, T, d):
+    """The HBM-bound launchers of the path (and the FP32 parity kernels) on the workload's shape, one GPU:
+    achieved GB/s = algorithmic bytes / CUDA-event time, against the measured HBM copy bandwidth."""
+    import torch
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    ops = pkg.ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    n, rows = B * H * T * d, B * H * T
+    f32, bf16 = torch.float32, torch.bfloat16
+    iters = max(5, min(args.steps, 50))
+
+    def timed(fn, copies=1):
+        for _ in range(3):
+            fn(0)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i % copies)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    # enough rotating copies of every buffer set to exceed L2
+    copies = max(2, math.ceil(2.0 * L2_BYTES / (24 * n)))
+    qkv = [ops.fill_normal_(torch.empty(B, T, 3 * H * d, device=dev), seed=50 + c) for c in range(copies)]
+    q32, k32, v32 = ([torch.empty(B, H, T, d, device=dev) for _ in range(copies)] for _ in range(3))
+    qb, kb, vb = ([torch.empty(B, H, T, d, device=dev, dtype=bf16) for _ in range(copies)] for _ in range(3))
+    merged = [torch.empty(B, T, H * d, device=dev) for _ in range(copies)]
+    out = []
+
+    def row(name, ref, ms, nbytes):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out.append({"launcher": name, "replaces": ref, "ms": round(ms, 4), "algorithmic_bytes": nbytes,
+                    "achieved_gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm"], 3)})
+
+    row("qkv_split_transpose_forward (FP32)", "attention.cu:381",
+        timed(lambda c: ops.qkv_split_transpose_forward(qkv[c], q32[c], k32[c], v32[c], B, T, H, d), copies), 24 * n)
+    row("qkv_split_transpose_backward (FP32)", "attention.cu:408",
+        timed(lambda c: ops.qkv_split_transpose_backward(q32[c], k32[c], v32[c], qkv[c], B, T, H, d), copies), 24 * n)
+    row("qkv split + BF16 conversion", "attention.cu:381",
+        timed(lambda c: ops.qkv_split_transpose_forward_bf16(qkv[c], qb[c], kb[c], vb[c], B, T, H, d), copies), 18 * n)
+    row("dqkv merge from BF16", "attention.cu:408",
+        timed(lambda c: ops.qkv_split_transpose_backward_bf16(qb[c], kb[c], vb[c], qkv[c], B, T, H, d), copies), 18 * n)
+    row("head_merge_transpose_forward (FP32)", "attention.cu:466",
+        timed(lambda c: ops.head_merge_transpose_forward(q32[c], merged[c], B, H, T, d), copies), 8 * n)
+    row("head_merge_transpose_backward (FP32)", "attention.cu:491",
+        timed(lambda c: ops.head_merge_transpose_backward(merged[c], q32[c], B, H, T, d), copies), 8 * n)
+    row("head merge from BF16", "attention.cu:466",
+        timed(lambda c: ops.head_merge_transpose_forward_bf16(qb[c], merged[c], B, H, T, d), copies), 6 * n)
+    D = torch.empty(B, H, T, device=dev)
+    row("attention_precompute_dot_do_o (FP32)", "attention.cu:679",
+        timed(lambda c: ops.attention_precompute_dot_do_o(q32[c], k32[c], D, B, H, T, d), copies), 8 * n + 4 * rows)
+    # materialised softmax of the non-tiled branch: one slab batch small enough to hold (rows x T floats)
+    Bs = max(1, min(B, (1 << 28) // (H * T * T)))
+    srows = Bs * H * T
+    scores = [ops.fill_normal_(torch.empty(srows, T, device=dev), seed=70 + c) for c in range(2)]
+    probs = [torch.empty(srows, T, device=dev) for _ in range(2)]
+    ms = timed(lambda c: ops.causal_softmax_forward(scores[c], probs[c], Bs, H, T, 0.125), 2)
+    row(f"causal_softmax_forward (B={Bs})", "attention.cu:435", ms, srows * T * 4 // 2 + srows * T * 4)  # reads j<=i, writes all
+    ms = timed(lambda c: ops.causal_softmax_backward(scores[c], probs[c], scores[1 - c], Bs, H, T, 0.125), 2)
+    row(f"causal_softmax_backward (B={Bs})", "attention.cu:450", ms, srows * T * 4 + srows * T * 4)  # reads 2 halves, writes all
+    # FP32 parity kernels: compute-bound SIMT, reported in TFLOP/s
+    o32, m32, l32 = torch.empty_like(q32[0]), torch.empty(B, H, T, device=dev), torch.empty(B, H, T, device=dev)
+    dq, dk, dv, ws = torch.empty_like(o32), torch.empty_like(o32), torch.empty_like(o32), torch.empty(B, H, T, device=dev)
+    ops.set_math_mode("fp32")
+    scale = 1.0 / math.sqrt(d)
+    iters = 3
+    ms_f = timed(lambda c: ops.tiled_causal_attention_forward(q32[0], k32[0], v32[0], o32, B, H, T, d, scale, m32, l32))
+    ms_b = timed(lambda c: ops.tiled_causal_attention_backward(q32[0], k32[0], v32[0], o32, merged[0].view(B, H, T, d), m32,
+                                                               l32, dq, dk, dv, ws, B, H, T, d, scale))
+    fl = flops(B, H, T, d)
+    print(json.dumps({
+        "suite": "path-kernels", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm"], "peak_source": peaks["source"],
+        "config": {"workload": workload_name(args, B, H, T, d), "l2": f"{copies} rotating buffer sets"},
+        "kernels": out,
+        "fp32_parity_mode": {"forward_ms": round(ms_f, 3), "backward_ms": round(ms_b, 3),
+                             "tflops": round(fl / ((ms_f + ms_b) * 1e-3) / 1e12, 3),
+                             "note": "SIMT FP32, exact expf: the <=1e-5 parity path, not the fast path"},
+    }), flush=True)
+
+
 def workload_name(args, B, H, T, d):
     return f"{args.workload}: causal attention fwd+bwd, B={B} H={H} T={T} d={d} per GPU, BF16, scale=1/sqrt(d)"
 
@@ -178,12 +263,18 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--suite", default="attention", choices=["attention", "path-kernels"],
+                    help="'path-kernels': time every other launcher of the path (layout, softmax, pre-pass, FP32 parity "
+                         "kernels) against the HBM roofline and print one JSON line with a table")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     B, H, T, d = WORKLOADS[args.workload]
 
     if args.impl == "reference":
         run_reference(args, B, H, T, d)
+        return
+    if args.suite == "path-kernels":
+        run_path_kernels(args, B, H, T, d)
         return
 
     import torch

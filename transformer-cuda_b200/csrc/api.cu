@@ -427,7 +427,13 @@ extern "C" int b200attn_dot_do_o_f32(const float* dO, const float* O, float* D, 
     long long rows = (long long)B * H * T;
     if (rows == 0) return B200ATTN_OK;
     REQUIRE_PTR(fn, dO); REQUIRE_PTR(fn, O); REQUIRE_PTR(fn, D);
-    RETURN_IF_CUDA(launch_dot_do_o_f32(dO, O, D, rows, d, (cudaStream_t)stream), fn);
+    // 16-byte loads with d/4 threads per row when the shape allows it, else one warp per row
+    const int tpr = d / 4;
+    const bool wide = (d % 4 == 0) && tpr <= 32 && (tpr & (tpr - 1)) == 0 && aligned16(dO) && aligned16(O);
+    if (wide)
+        RETURN_IF_CUDA(launch_bwd_prepass<float>(O, dO, nullptr, nullptr, nullptr, D, nullptr, nullptr, rows, d, (cudaStream_t)stream), fn);
+    else
+        RETURN_IF_CUDA(launch_dot_do_o_f32(dO, O, D, rows, d, (cudaStream_t)stream), fn);
     return B200ATTN_OK;
 }
 
@@ -446,7 +452,14 @@ extern "C" int b200attn_bwd_f32(const float* q, const float* k, const float* v, 
     REQUIRE_PTR(fn, workspace);
     if (g_math_mode.load() == B200ATTN_MATH_FP32) {
         if (d > 256) return fail(B200ATTN_ERR_UNSUPPORTED, "%s: FP32 mode supports d <= 256, got %d", fn, d);
-        RETURN_IF_CUDA(launch_dot_do_o_f32(dO, o, workspace, rows, d, stream), "D pre-pass");
+        {
+            const int tpr = d / 4;
+            const bool wide = (d % 4 == 0) && tpr <= 32 && (tpr & (tpr - 1)) == 0 && aligned16(dO) && aligned16(o);
+            if (wide)
+                RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, nullptr, nullptr, nullptr, workspace, nullptr, nullptr, rows, d, stream), "D pre-pass");
+            else
+                RETURN_IF_CUDA(launch_dot_do_o_f32(dO, o, workspace, rows, d, stream), "D pre-pass");
+        }
         RETURN_IF_CUDA(launch_attn_bwd_f32(q, k, v, dO, m, l, workspace, dq, dk, dv, BH, T, d, scale, stream), fn);
         return B200ATTN_OK;
     }

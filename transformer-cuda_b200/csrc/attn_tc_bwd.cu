@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     const float l4[4] = {ls.x, ls.y, ls.z, ls.w};
 #pragma unroll
                     for (int y = 0; y < 4; ++y) {
-                        float e = fast_exp2(fmaf(__uint_as_float(sv[x + y]), scale_log2, -l4[y]));
+                        float e = mixed_exp2(fmaf(__uint_as_float(sv[x + y]), scale_log2, -l4[y]), y);
                         if (diag && (c + x + y) < r) e = 0.f;  // query before this key: masked
                         p[cc + x + y] = e;
                     }

@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
             uint32_t pk[kBN / 2];
 #pragma unroll
             for (int c = 0; c < kBN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_ref));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_ref));
+                const float p0 = mixed_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_ref), c);
+                const float p1 = mixed_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_ref), c + 1);
                 sum += p0 + p1;
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }

@@ -287,6 +287,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 2^x on the FMA / integer pipes, for x <= ~100 (larger arguments do not occur: scores are taken
+// relative to a running maximum): round-to-nearest split x = i + f with the 1.5*2^23 trick, a
+// degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (relative error 2.1e-4, far below BF16
+// resolution), and i added into the exponent field. Arguments below -126 (masked scores) give 2^-126.
+// Used for a fraction of the exponentials so that the 16-per-clock MUFU unit is not the only path.
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -126.0f);
+    const float xf = __fadd_rn(x, 12582912.0f);
+    const float f = __fsub_rn(x, __fsub_rn(xf, 12582912.0f));
+    float p = fmaf(f, 0.05484806f, 0.24180646f);
+    p = fmaf(f, p, 0.69324815f);
+    p = fmaf(f, p, 0.99998868f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(xf) << 23));
+}
+// Fraction of exponentials sent to poly_exp2: element index e uses it when (e & 3) == 3.
+// OFF by default: measured on B200 with 25 % of the exponentials on the polynomial, both kernels got
+// 4-7 % SLOWER (forward T=8192 d=128 0.583 -> 0.626 ms, backward 1.474 -> 1.584 ms): the softmax /
+// compute warps are bound by instruction issue, not by the MUFU unit, and the polynomial costs nine
+// issue slots against two.
+#ifndef B200ATTN_POLY_EXP2
+#define B200ATTN_POLY_EXP2 0
+#endif
+__device__ __forceinline__ float mixed_exp2(float x, int e) {
+#if B200ATTN_POLY_EXP2
+    return ((e & 3) == 3) ? poly_exp2(x) : fast_exp2(x);
+#else
+    return fast_exp2(x);
+#endif
+}
+
 // Named barrier over a subset of the CTA's warps (id 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
