@@ -165,6 +165,41 @@ def run_reference(args, B, H, T, d):
     }), flush=True)
 
 
+def run_gpt_step(args):
+    """Config 4: full synthetic GPT training step (L=12, C=768, H=12, d_ff=3072, V=50257, T=1024, per-GPU B=16,
+    AdamW), data-parallel with one NCCL all-reduce of the gradient buffer per step. The step is the reference's
+    own model code linked against this engine (transformer-cuda_b200/harness/gpt_step_dp.cu; binary prebuilt by
+    oracle/Makefile where the reference checkout exists). Launched by torchrun, every bench.py rank starts the
+    binary as its rank's process (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_PORT are inherited); rank 0 relays the
+    JSON line. `--impl reference` runs the same harness linked against the reference's own attention kernels."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    name = "gpt_step_dp_ref" if args.impl == "reference" else "gpt_step_dp_b200"
+    exe = os.path.join(ROOT, "oracle", "_ref", name)
+    if not os.path.exists(exe):
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "metric": "gpt_step_tokens_per_s",
+                              "unavailable": f"{name} is built from the reference checkout by `make -C oracle`; not present here"}))
+        return
+    steps = max(1, min(args.steps, 20))
+    env = dict(os.environ)
+    env.setdefault("B200ATTN_MATH", "bf16")  # attention through the tcgen05 kernels (the reference arm ignores it)
+    res = subprocess.run([exe, "--steps", str(steps), "--warmup", str(min(args.warmup, 3))], env=env, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise SystemExit(f"{name} failed on rank {rank}: {res.stderr[-2000:]}")
+    if rank != 0:
+        return
+    child = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    line = {"metric": "gpt_step_tokens_per_s", "value": child["value"], "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": min(args.warmup, 3), "ms_per_step": child["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 model, bf16 attention" if args.impl != "reference" else "f32",
+            "data": "synthetic", "impl": args.impl,
+            "config": {"workload": "c4: GPT training step L=12 C=768 H=12 d_ff=3072 V=50257 T=1024, per-GPU B=16, AdamW, "
+                                   "data-parallel NCCL all-reduce of gradients", **child["config"], "attention": child["attention"]},
+            "loss_after_last_step": child["loss"]}
+    print(json.dumps(line), flush=True)
+
+
 def run_path_kernels(args, B, H, T, d):
     """The HBM-bound launchers of the path (and the FP32 parity kernels) on the workload's shape, one GPU:
     achieved GB/s = algorithmic bytes / CUDA-event time, against the measured HBM copy bandwidth."""
@@ -260,7 +295,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4"],
+                    help="c2 (default), c3, c5_*: the attention path; c4: the data-parallel GPT training step around it")
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--suite", default="attention", choices=["attention", "path-kernels"],
@@ -268,6 +304,9 @@ def main():
                          "kernels) against the HBM roofline and print one JSON line with a table")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "c4":
+        run_gpt_step(args)
+        return
     B, H, T, d = WORKLOADS[args.workload]
 
     if args.impl == "reference":
