@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
-SOURCES = ["api.cu", "launch_api.cu", "layout_kernels.cu", "softmax_kernels.cu", "attn_f32.cu", "attn_tc_fwd.cu", "attn_tc_fwd_short.cu",
+SOURCES = ["api.cu", "launch_api.cu", "layout_kernels.cu", "softmax_kernels.cu", "attn_f32.cu", "attn_f32_tiled.cu", "attn_tc_fwd.cu", "attn_tc_fwd_short.cu",
            "attn_tc_bwd.cu", "static_scratch.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]

@@ -239,6 +239,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 cudaError_t launch_attn_fwd_f32(const float* q, const float* k, const float* v, float* out, float* m_out, float* l_out,
                                 int BH, int T, int d, float scale, cudaStream_t stream) {
     if (BH == 0 || T == 0) return cudaSuccess;
+    if (attn_f32_tiled_supported(d, q, k, v, q))
+        return launch_attn_fwd_f32_tiled(q, k, v, out, m_out, l_out, BH, T, d, scale, stream);
     bool vec = (d % 4 == 0) && aligned16(q) && aligned16(k);
     dim3 grid((T + kWarps - 1) / kWarps, BH);
     attn_fwd_f32_kernel<<<grid, kWarps * 32, 0, stream>>>(q, k, v, out, m_out, l_out, T, d, scale, vec);
@@ -256,6 +258,8 @@ cudaError_t launch_attn_bwd_f32(const float* q, const float* k, const float* v, 
                                 const float* l, const float* D, float* dq, float* dk, float* dv, int BH, int T, int d,
                                 float scale, cudaStream_t stream) {
     if (BH == 0 || T == 0) return cudaSuccess;
+    if (attn_f32_tiled_supported(d, q, k, v, dO))
+        return launch_attn_bwd_f32_tiled(q, k, v, dO, m, l, D, dq, dk, dv, BH, T, d, scale, stream);
     bool vec = (d % 4 == 0) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(dO);
     dim3 grid((T + kWarps - 1) / kWarps, BH);
     attn_bwd_dq_f32_kernel<<<grid, kWarps * 32, 0, stream>>>(q, k, v, dO, m, l, D, dq, T, d, scale, vec);

@@ -41,6 +41,15 @@ cudaError_t launch_attn_bwd_f32(const float* q, const float* k, const float* v, 
                                 const float* l, const float* D, float* dq, float* dk, float* dv, int BH, int T, int d,
                                 float scale, cudaStream_t stream);
 
+// attn_f32_tiled.cu: shared-memory tiled variants for d in {32, 64, 128} with 16-byte aligned inputs;
+// launch_attn_fwd_f32 / launch_attn_bwd_f32 pick them when attn_f32_tiled_supported() says so.
+bool attn_f32_tiled_supported(int d, const void* a, const void* b, const void* c, const void* e);
+cudaError_t launch_attn_fwd_f32_tiled(const float* q, const float* k, const float* v, float* out, float* m_out,
+                                      float* l_out, int BH, int T, int d, float scale, cudaStream_t stream);
+cudaError_t launch_attn_bwd_f32_tiled(const float* q, const float* k, const float* v, const float* dO, const float* m,
+                                      const float* l, const float* D, float* dq, float* dk, float* dv, int BH, int T,
+                                      int d, float scale, cudaStream_t stream);
+
 // ------------------------------------------------------------------ attn_tc_fwd.cu / attn_tc_bwd.cu (tcgen05)
 struct TcFwdArgs {
     CUtensorMap map_q, map_k, map_v, map_o;  // (d, T, BH) BF16 tensors, box 64 x 128 x 1, 128-byte swizzle
