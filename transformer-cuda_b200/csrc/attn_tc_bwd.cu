@@ -32,8 +32,8 @@
 
 #ifdef B200ATTN_TRACE
 // Debug builds only: clock64() stamps of the first CTA's MMA warp and compute thread 0, read back by
-// b200attn_debug_read_bwd_trace(). Slot = role * 2048 + iteration * 16 + point.
-__device__ long long g_bwd_trace[4096];
+// b200attn_debug_read_bwd_trace(). Slot = role * 2048 + iteration * 16 + point (role 2: compute thread 255).
+__device__ long long g_bwd_trace[6144];
 #define BWD_TRACE(role, it, point)                                                              \
     do {                                                                                        \
         if (blockIdx.x == 0 && (it) < 128) g_bwd_trace[(role) * 2048 + (it) * 16 + (point)] = clock64(); \
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             const int qs = it % Cfg::kQStages;
             mbar_wait(&bars.q_full[qs], (it / Cfg::kQStages) & 1, &abort_flag, a.fault_word, 0x50);
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t q_kmaj = make_smem_desc_sw128(smem_u32(sQ + qs * Cfg::kTileBytes), 0, 1024);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             if (Cfg::kDqAliased && it > 0)  // the dQ partial of the previous tile sits in these columns
                 mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x52);
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t do_kmaj = make_smem_desc_sw128(smem_u32(sDO + os * Cfg::kTileBytes), 0, 1024);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             mbar_wait(&bars.p_ready, it & 1, &abort_flag, a.fault_word, 0x55);
             tc_fence_after();
             if (lane == 0) BWD_TRACE(0, it, 0);
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t do_mnmaj = make_smem_desc_sw128(smem_u32(sDO + os * Cfg::kTileBytes), kAtomBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             if (!Cfg::kDqAliased && it > 0)  // previous dQ partial must have been read out of its columns
                 mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x57);
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t q_mnmaj = make_smem_desc_sw128(smem_u32(sQ + qs * Cfg::kTileBytes), kAtomBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk) {
@@ -313,15 +313,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
         auto dq_fetch = [&](int it) {  // TMEM -> registers; frees the dQ columns for the MMA warp
             mbar_wait(&bars.dq_full, it & 1, &abort_flag, a.fault_word, 0x60);
             tc_fence_after();
+            if (tid == 0) BWD_TRACE(1, it + 1, 11);
 #pragma unroll
             for (int c = 0; c < D / 2; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDQ + half * (D / 2) + c), &dqv[c]);
             tmem_wait_ld();
+            if (tid == 0) BWD_TRACE(1, it + 1, 12);
             tc_fence_before();
             mbar_arrive(&bars.dq_empty);
         };
         auto dq_send = [&](int it, int rd) {  // registers -> staging -> reduce-add, 32 columns per thread
             if (tid == 0) tma_store_wait_read();  // earlier reductions have finished reading the staging tile
             named_bar_sync(2, kComputeThreads);
+            if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 13);
             uint8_t* stage = sDQ + half * kAtomBytes;
 #pragma unroll
             for (int x = 0; x < 32; x += 4)
@@ -329,6 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     make_uint4(dqv[rd * 32 + x], dqv[rd * 32 + x + 1], dqv[rd * 32 + x + 2], dqv[rd * 32 + x + 3]);
             fence_proxy_async_smem();
             named_bar_sync(2, kComputeThreads);
+            if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 14);
             if (tid == 0) {
                 tma_reduce_add_3d(&a.map_dq_acc, sDQ, rd * 32, (jt + it) * kBQ, bh);
                 tma_reduce_add_3d(&a.map_dq_acc, sDQ + kAtomBytes, D / 2 + rd * 32, (jt + it) * kBQ, bh);
@@ -348,6 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             const int i = jt + it;
             const int buf = it & 1;
             if (tid == 0) BWD_TRACE(1, it, 0);
+            if (tid == 255) BWD_TRACE(2, it, 0);
             {   // per-query statistics of this tile: column c of the transposed tiles is query i*128 + c
                 if (half == 0) s_lse[buf][r] = stat_next;  // +inf for queries beyond T -> P = 0
                 else s_D[buf][r] = stat_next;
@@ -400,6 +405,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             tc_fence_before();
             mbar_arrive(&bars.p_ready);
             if (tid == 0) BWD_TRACE(1, it, 3);
+            if (tid == 255) BWD_TRACE(2, it, 3);
 
             // ---- previous tile's dQ partial (its MMA ran while the exponentials above were computed)
             if (it > 0) {
@@ -407,11 +413,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 dq_send(it - 1, 0);
             }
             if (tid == 0) BWD_TRACE(1, it, 4);
+            if (tid == 255) BWD_TRACE(2, it, 4);
 
             // ---- dS^T
             mbar_wait(&bars.dp_full, it & 1, &abort_flag, a.fault_word, 0x62);
             tc_fence_after();
             if (tid == 0) BWD_TRACE(1, it, 5);
+            if (tid == 255) BWD_TRACE(2, it, 5);
 #pragma unroll
             for (int cc = 0; cc < kBQ / 2; cc += 32) {
                 const int c = c_begin + cc;
@@ -439,6 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             tc_fence_before();
             mbar_arrive(&bars.ds_ready);
             if (tid == 0) BWD_TRACE(1, it, 6);
+            if (tid == 255) BWD_TRACE(2, it, 6);
             if (Cfg::kDqRounds == 2 && it > 0) dq_send(it - 1, 1);  // second half of the previous partial
         }
 #ifdef B200ATTN_TRACE

@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             mbar_wait(&bars.k_full[ks], (j / Cfg::kKStages) & 1, &abort_flag, a.fault_word, 0x21);
             tc_fence_after();
             if (lane == 0) FWD_TRACE(0, j, 0);
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + ks * Cfg::kTileBytes), 0, 1024);
                 const uint32_t d_tmem = tmem + Cfg::kColS + (j % Cfg::kSBuffers) * 128;
 #pragma unroll
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             mbar_wait(&bars.p_full[b], (j / Cfg::kSBuffers) & 1, &abort_flag, a.fault_word, 0x23);
             tc_fence_after();
             if (lane == 0) FWD_TRACE(0, j, 2);
-            if (lane == 0) {
+            if (elect_one()) {
                 // V tile: rows = key index (the MMA's K), 64-column atoms along the head dim (its N)
                 const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + vs * Cfg::kTileBytes), kAtomBytes, 1024);
                 const uint32_t p_tmem = tmem + Cfg::kColS + b * 128;
@@ -235,9 +235,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
                 for (int c = 0; c < kHalfCols; ++c)
                     if (c_begin + c > r) sv[c] = 0xff800000u;  // -inf
             }
-            float mx = -INFINITY;
+            // four independent chains instead of one running maximum of 64 dependent instructions
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < kHalfCols; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+            for (int c = 0; c < kHalfCols; c += 4) {
+#pragma unroll
+                for (int y = 0; y < 4; ++y) mx4[y] = fmaxf(mx4[y], __uint_as_float(sv[c + y]));
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // row maximum over both halves (the buffer alternates with the tile parity, so one barrier per tile is enough)
             s_xchg[j & 1][half][r] = mx;
             named_bar_sync(1, kSoftmaxThreads);
@@ -250,16 +255,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
                 alpha = fast_exp2(m_ref - m_true);  // 0 on the first tile
                 m_ref = m_true;
             }
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[kHalfCols / 2];
 #pragma unroll
             for (int c = 0; c < kHalfCols; c += 2) {
                 const float p0 = mixed_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_ref), c);
                 const float p1 = mixed_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_ref), c + 1);
-                sum += p0 + p1;
+                sum4[(c >> 1) & 3] += p0 + p1;
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (tid == 0) FWD_TRACE(1, j, 4);
             // each half packs its P into the first 32 columns of its OWN 64 score columns
             tmem_st32(tmem_addr(tmem, lane_base, s_col), pk);

@@ -24,13 +24,50 @@
 //              score buffer, and O += P_j V_j (A from TMEM, V as an MN-major shared-memory
 //              operand, so no transpose is materialised).
 //
-// A CTA uses 256 TMEM columns ([0,128) S/P, [128,128+D) O) and at most 96 KB of shared memory, so
-// two CTAs are resident per SM: while one CTA's softmax warps work on a tile, the other CTA's MMAs
-// and loads run, and the prologue / epilogue of one overlaps the main loop of the other.
+// A CTA uses 256 TMEM columns and at most 96 KB of shared memory, so two CTAs are resident per SM:
+// while one CTA's softmax warps work on a tile, the other CTA's MMAs and loads run, and the
+// prologue / epilogue of one overlaps the main loop of the other.
+//   D = 128: [0,128) S with P written over it, [128,256) O. S_{j+1} can only be issued behind P_j V_j.
+//   D = 64:  [0,128) S, [128,192) O, [192,256) P. The softmax threads pull a whole score row into
+//            registers and release the score buffer at once (s_free), so S_{j+1} = Q K_{j+1}^T runs
+//            under the exponentials of tile j and the softmax threads never wait for the tensor
+//            pipe in steady state; P_j V_j runs under the exponentials of tile j+1.
 // Every mbarrier wait has an iteration limit (tc_common.cuh); a wait that gives up sets the fault
 // word and the kernel still runs to its end and frees its TMEM.
 #include "kernels.cuh"
 #include "tc_common.cuh"
+
+#ifdef B200ATTN_TRACE
+// Debug builds only. Per-CTA life line: {globaltimer at start, first scores ready, loop end, exit, smid, key tiles};
+// and clock64 stamps of CTA 0's softmax thread 0 per tile: {s_full seen, loaded, exps done, arrive}.
+__device__ long long g_fwds_cta_trace[8 * 4096];
+__device__ long long g_fwds_tile_trace[8 * 64];
+extern "C" int b200attn_debug_read_fwds_trace(long long* cta, long long* tile) {
+    cudaError_t e = cudaMemcpyFromSymbol(cta, g_fwds_cta_trace, sizeof(g_fwds_cta_trace));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(tile, g_fwds_tile_trace, sizeof(g_fwds_tile_trace));
+    return (int)e;
+}
+__device__ __forceinline__ long long fwds_globaltimer() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define FWDS_CTA_TRACE(slot, value)                                                  \
+    do {                                                                             \
+        if (blockIdx.x < 4096) g_fwds_cta_trace[blockIdx.x * 8 + (slot)] = (value);  \
+    } while (0)
+#define FWDS_TILE_TRACE(j, point)                                                                    \
+    do {                                                                                             \
+        if (blockIdx.x == 0 && threadIdx.x == 0 && (j) < 64) g_fwds_tile_trace[(j) * 8 + (point)] = clock64(); \
+    } while (0)
+#else
+#define FWDS_CTA_TRACE(slot, value) \
+    do {                            \
+    } while (0)
+#define FWDS_TILE_TRACE(j, point) \
+    do {                          \
+    } while (0)
+#endif
 
 namespace b200attn {
 namespace {
@@ -50,13 +87,15 @@ struct FwdCfg {
     static constexpr int kStages = (D == 64) ? 2 : 1;
     static constexpr int kSmemBytes = kTileBytes * (1 + 2 * kStages);  // dynamic buffer is declared 1024-aligned
     static constexpr uint32_t kTmemCols = 256;
+    static constexpr bool kSeparateP = (D == 64);  // P in its own columns: the score buffer is free once loaded
     static constexpr uint32_t kColS = 0, kColO = 128;
+    static constexpr uint32_t kColP = kSeparateP ? 192 : 0;
 };
 
 struct FwdBarriers {
     uint64_t q_full;
     uint64_t k_full[3], v_full[3], k_empty[3], v_empty[3];
-    uint64_t s_full, p_full;
+    uint64_t s_full, p_full, s_free;
     uint64_t o_done;
 };
 
@@ -82,6 +121,15 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
     const int bh = a.tile_major_order ? int(blockIdx.x % a.BH) : int(blockIdx.x / n_q_tiles);
     const int qt = n_q_tiles - 1 - (a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_q_tiles));
     const int n_kv = qt + 1;                                  // key tiles 0..qt; qt is the diagonal tile
+#ifdef B200ATTN_TRACE
+    if (tid == 0) {
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        FWDS_CTA_TRACE(0, fwds_globaltimer());
+        FWDS_CTA_TRACE(4, (long long)smid);
+        FWDS_CTA_TRACE(5, (long long)n_kv);
+    }
+#endif
 
     if (tid == 0) {
         mbar_init(&bars.q_full, 1);
@@ -93,6 +141,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
         }
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.p_full, kSoftmaxThreads);
+        mbar_init(&bars.s_free, kSoftmaxThreads);
         mbar_init(&bars.o_done, 1);
         abort_flag = 0;
         if ((smem_u32(smem) & 1023u) != 0 && a.fault_word) atomicCAS(a.fault_word, 0u, kFaultWaitTimeout | 0xA10u);
@@ -136,13 +185,11 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
         constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, D, 0, 1);
         const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 0, 1024);
         mbar_wait(&bars.q_full, 0, &abort_flag, a.fault_word, 0x20);
-        for (int j = 0; j < n_kv; ++j) {
+        auto issue_qk = [&](int j) {  // S = Q K_j^T
             const int s = j % Cfg::kStages;
-            const uint32_t ring_phase = (j / Cfg::kStages) & 1;
-            // S = Q K_j^T (the score buffer is free: P_{j-1} V_{j-1} was issued before, and MMAs run in order)
-            mbar_wait(&bars.k_full[s], ring_phase, &abort_flag, a.fault_word, 0x21);
+            mbar_wait(&bars.k_full[s], (j / Cfg::kStages) & 1, &abort_flag, a.fault_word, 0x21);
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
                 const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + s * Cfg::kTileBytes), 0, 1024);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -153,16 +200,31 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
                 tc_commit(&bars.s_full);
             }
             __syncwarp();
+        };
+        if (Cfg::kSeparateP) issue_qk(0);
+        for (int j = 0; j < n_kv; ++j) {
+            const int s = j % Cfg::kStages;
+            const uint32_t ring_phase = (j / Cfg::kStages) & 1;
+            if (Cfg::kSeparateP) {
+                // the softmax threads hold S_j in registers: the next scores run under their exponentials
+                if (j + 1 < n_kv) {
+                    mbar_wait(&bars.s_free, j & 1, &abort_flag, a.fault_word, 0x24);
+                    issue_qk(j + 1);
+                }
+            } else {
+                // the score buffer is free: P_{j-1} V_{j-1} was issued before, and MMAs run in order
+                issue_qk(j);
+            }
             // O += P_j V_j
             mbar_wait(&bars.v_full[s], ring_phase, &abort_flag, a.fault_word, 0x22);
             mbar_wait(&bars.p_full, j & 1, &abort_flag, a.fault_word, 0x23);
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one()) {
                 // V tile: rows = key index (the MMA's K), 64-column atoms along the head dim (its N)
                 const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + s * Cfg::kTileBytes), kAtomBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    tc_mma_ts(tmem + Cfg::kColO, tmem + Cfg::kColS + kk * 8, desc_advance(v_desc, kk * 2048), idesc_pv,
+                    tc_mma_ts(tmem + Cfg::kColO, tmem + Cfg::kColP + kk * 8, desc_advance(v_desc, kk * 2048), idesc_pv,
                               (j > 0) || (kk > 0));
                 tc_commit(&bars.v_empty[s]);
                 tc_commit(&bars.o_done);
@@ -183,21 +245,35 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
         float l_run = 0.f;
         for (int j = 0; j < n_kv; ++j) {
             constexpr uint32_t s_col = Cfg::kColS;
-            // s_full(j) also means P.V of tile j-1 has retired (MMAs run in order), so O is up to date
+            // D = 128: s_full(j) also means P.V of tile j-1 has retired (MMAs run in order), so O is up to date
             mbar_wait(&bars.s_full, j & 1, &abort_flag, a.fault_word, 0x30);
             tc_fence_after();
+#ifdef B200ATTN_TRACE
+            if (tid == 0 && j == 0) FWDS_CTA_TRACE(1, fwds_globaltimer());
+#endif
+            FWDS_TILE_TRACE(j, 0);
             uint32_t sv[kBN];
 #pragma unroll
             for (int c = 0; c < kBN; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, s_col + c), &sv[c]);
             tmem_wait_ld();
+            if (Cfg::kSeparateP) {  // the whole row is in registers: hand the score buffer back
+                tc_fence_before();
+                mbar_arrive(&bars.s_free);
+            }
+            FWDS_TILE_TRACE(j, 1);
             if (j == qt) {  // diagonal tile: key c is visible to query r iff c <= r
 #pragma unroll
                 for (int c = 0; c < kBN; ++c)
                     if (c > r) sv[c] = 0xff800000u;  // -inf
             }
-            float mx = -INFINITY;
+            // four independent chains: a single running maximum is 128 dependent instructions
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+            for (int c = 0; c < kBN; c += 4) {
+#pragma unroll
+                for (int y = 0; y < 4; ++y) mx4[y] = fmaxf(mx4[y], __uint_as_float(sv[c + y]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             m_true = fmaxf(m_true, mx * scale_log2);
             const bool move = (j == 0) || (m_true - m_ref > kRescaleThreshold);
             float alpha = 1.0f;
@@ -205,18 +281,23 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
                 alpha = fast_exp2(m_ref - m_true);  // 0 on the first tile
                 m_ref = m_true;
             }
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[kBN / 2];
 #pragma unroll
             for (int c = 0; c < kBN; c += 2) {
                 const float p0 = mixed_exp2(fmaf(__uint_as_float(sv[c]), scale_log2, -m_ref), c);
                 const float p1 = mixed_exp2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -m_ref), c + 1);
-                sum += p0 + p1;
+                sum4[(c >> 1) & 3] += p0 + p1;
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            FWDS_TILE_TRACE(j, 2);
+            if (Cfg::kSeparateP && j > 0) {  // P_{j-1} V_{j-1} must have read the P columns (and updated O)
+                mbar_wait(&bars.o_done, (j - 1) & 1, &abort_flag, a.fault_word, 0x31);
+                tc_fence_after();
+            }
 #pragma unroll
-            for (int c = 0; c < kBN / 2; c += 32) tmem_st32(tmem_addr(tmem, lane_base, s_col + c), &pk[c]);
+            for (int c = 0; c < kBN / 2; c += 32) tmem_st32(tmem_addr(tmem, lane_base, Cfg::kColP + c), &pk[c]);
             if (j > 0 && __any_sync(0xffffffffu, move)) {
                 // bring the O accumulator to the new reference (rows that did not move use alpha = 1)
 #pragma unroll
@@ -232,10 +313,15 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars.p_full);
+            FWDS_TILE_TRACE(j, 3);
         }
+#ifdef B200ATTN_TRACE
+        if (tid == 0) FWDS_CTA_TRACE(2, fwds_globaltimer());
+#endif
         // ---- epilogue: O / l
         mbar_wait(&bars.o_done, (n_kv - 1) & 1, &abort_flag, a.fault_word, 0x32);
         tc_fence_after();
+        FWDS_TILE_TRACE(n_kv, 0);
         const float inv_l = 1.0f / l_run;
         const int row_g = qt * kBM + r;
         const long long stat_idx = (long long)bh * a.T + row_g;
@@ -286,6 +372,9 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
     tc_fence_before();
     __syncthreads();
     if (warp == 4) tmem_dealloc(tmem, Cfg::kTmemCols);
+#ifdef B200ATTN_TRACE
+    if (tid == 0) FWDS_CTA_TRACE(3, fwds_globaltimer());
+#endif
 }
 
 template <int D, bool OUT_F32>
