@@ -269,8 +269,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             if (lane == 0) BWD_TRACE(0, it, 3);
             // dS^T(it) done means dP^T(it) has been consumed: with dQ in its own columns the next dP^T can go first
             if (!Cfg::kDqAliased && it + 1 < n_it) issue_dp(it + 1);
-            if (!Cfg::kDqAliased && it > 0)  // previous dQ partial must have been read out of its columns
-                mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x57);
             tc_fence_after();
             if (elect_one()) {
                 const uint64_t q_mnmaj = make_smem_desc_sw128(smem_u32(sQ + qs * Cfg::kTileBytes), kAtomBytes, 1024);
@@ -281,6 +279,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                               (it > 0) || (kk > 0));
                 }
                 tc_commit(&bars.q_empty[qs]);  // S^T(it) and dK(it) were the readers of this Q tile
+            }
+            __syncwarp();
+            if (!Cfg::kDqAliased && it > 0) {  // previous dQ partial must have been read out of its columns
+                mbar_wait(&bars.dq_empty, (it - 1) & 1, &abort_flag, a.fault_word, 0x57);
+                tc_fence_after();
+            }
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < kBKV / 16; ++kk)
                     tc_mma_ss(tmem + Cfg::kColDQ, desc_advance(ds_mnmaj, kk * 2048), desc_advance(k_mnmaj, kk * 2048),
@@ -322,6 +327,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             mbar_arrive(&bars.dq_empty);
         };
         auto dq_send = [&](int it, int rd) {  // registers -> staging -> reduce-add, 32 columns per thread
+#ifdef B200ATTN_DQ_RED
+            {   // experiment: vector reductions straight from registers, no staging
+                const int q_row = (jt + it) * kBQ + r;
+                if (q_row < a.T) {
+                    float* dst = a.dq_acc + ((long long)bh * a.T + q_row) * D + half * (D / 2) + rd * 32;
+#pragma unroll
+                    for (int x = 0; x < 32; x += 4)
+                        red_add_v4(dst + x, __uint_as_float(dqv[rd * 32 + x]), __uint_as_float(dqv[rd * 32 + x + 1]),
+                                   __uint_as_float(dqv[rd * 32 + x + 2]), __uint_as_float(dqv[rd * 32 + x + 3]));
+                }
+                named_bar_sync(2, kComputeThreads);
+                return;
+            }
+#endif
             if (tid == 0) tma_store_wait_read();  // earlier reductions have finished reading the staging tile
             named_bar_sync(2, kComputeThreads);
             if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 13);
@@ -341,27 +360,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
         };
 
         // statistics of the first query tile; later tiles are fetched one iteration ahead
-        float stat_next;
-        {
-            const int q_g = jt * kBQ + r;
-            stat_next = (half == 0) ? ((q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY)
-                                    : ((q_g < a.T) ? a.D[stat_base + q_g] : 0.f);
-        }
+        // Per-query statistics (column c of the transposed tiles is query i*128 + c): half 0 threads carry
+        // lse2[q = r], half 1 threads D[q = r], fetched one tile ahead and stored into the other buffer
+        // at the END of a step, where the barrier of the dQ drain publishes them; so no barrier of their
+        // own stands in front of the exponentials.
+        auto load_stat = [&](int i) -> float {
+            const int q_g = i * kBQ + r;
+            return (half == 0) ? ((q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY)  // +inf beyond T -> P = 0
+                               : ((q_g < a.T) ? a.D[stat_base + q_g] : 0.f);
+        };
+        auto store_stat = [&](int buf, float v) {
+            if (half == 0) s_lse[buf][r] = v;
+            else s_D[buf][r] = v;
+        };
+        store_stat(0, load_stat(jt));
+        float stat_next = (n_it > 1) ? load_stat(jt + 1) : 0.f;
+        named_bar_sync(1, kComputeThreads);
 
         for (int it = 0; it < n_it; ++it) {
             const int i = jt + it;
             const int buf = it & 1;
             if (tid == 0) BWD_TRACE(1, it, 0);
             if (tid == 255) BWD_TRACE(2, it, 0);
-            {   // per-query statistics of this tile: column c of the transposed tiles is query i*128 + c
-                if (half == 0) s_lse[buf][r] = stat_next;  // +inf for queries beyond T -> P = 0
-                else s_D[buf][r] = stat_next;
-                const int q_g = (i + 1) * kBQ + r;  // prefetch for the next tile
-                if (it + 1 < n_it)
-                    stat_next = (half == 0) ? ((q_g < a.T) ? a.lse2[stat_base + q_g] : INFINITY)
-                                            : ((q_g < a.T) ? a.D[stat_base + q_g] : 0.f);
-            }
-            named_bar_sync(1, kComputeThreads);
 
             // ---- P^T
             if (tid == 0) BWD_TRACE(1, it, 1);
@@ -407,8 +427,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             if (tid == 0) BWD_TRACE(1, it, 3);
             if (tid == 255) BWD_TRACE(2, it, 3);
 
-            // ---- previous tile's dQ partial (its MMA ran while the exponentials above were computed)
-            if (it > 0) {
+            // ---- d = 128: the previous tile's dQ partial sits in the dP^T columns and has to leave before
+            // dP^T of this tile can be produced (its MMA ran while the exponentials above were computed)
+            if (Cfg::kDqAliased && it > 0) {
                 dq_fetch(it - 1);
                 dq_send(it - 1, 0);
             }
@@ -420,26 +441,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             tc_fence_after();
             if (tid == 0) BWD_TRACE(1, it, 5);
             if (tid == 255) BWD_TRACE(2, it, 5);
+            {
+                // both TMEM loads and the statistics are requested before the single wait: chunk-by-chunk
+                // (load, wait, compute, store) exposed the load latency twice and measured 860 cycles
+                // for this pass against 490 in this form
+                uint32_t dv[kBQ / 2];
 #pragma unroll
-            for (int cc = 0; cc < kBQ / 2; cc += 32) {
-                const int c = c_begin + cc;
-                uint32_t dv[32];
-                tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDP + c), dv);
+                for (int cc = 0; cc < kBQ / 2; cc += 32) tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDP + c_begin + cc), &dv[cc]);
+                float dd[kBQ / 2];
+#pragma unroll
+                for (int x = 0; x < kBQ / 2; x += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(&s_D[buf][c_begin + x]);
+                    dd[x] = t.x, dd[x + 1] = t.y, dd[x + 2] = t.z, dd[x + 3] = t.w;
+                }
                 tmem_wait_ld();
 #pragma unroll
-                for (int x = 0; x < 32; x += 8) {
-                    const float4 d0 = *reinterpret_cast<const float4*>(&s_D[buf][c + x]);
-                    const float4 d1 = *reinterpret_cast<const float4*>(&s_D[buf][c + x + 4]);
-                    const float dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+                for (int x = 0; x < kBQ / 2; x += 8) {
                     float ds[8];
 #pragma unroll
-                    for (int y = 0; y < 8; ++y) ds[y] = p[cc + x + y] * (__uint_as_float(dv[x + y]) - dd[y]) * a.scale;
+                    for (int y = 0; y < 8; ++y) ds[y] = (p[x + y] * a.scale) * (__uint_as_float(dv[x + y]) - dd[x + y]);
                     uint4 w;
                     w.x = pack_bf16x2(ds[0], ds[1]);
                     w.y = pack_bf16x2(ds[2], ds[3]);
                     w.z = pack_bf16x2(ds[4], ds[5]);
                     w.w = pack_bf16x2(ds[6], ds[7]);
-                    const int qc = c + x;  // first query column of this 16-byte chunk
+                    const int qc = c_begin + x;  // first query column of this 16-byte chunk
                     *reinterpret_cast<uint4*>(sDS + (qc >> 6) * kAtomBytes + swz128(r, (qc & 63) >> 3)) = w;
                 }
             }
@@ -448,7 +474,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             mbar_arrive(&bars.ds_ready);
             if (tid == 0) BWD_TRACE(1, it, 6);
             if (tid == 255) BWD_TRACE(2, it, 6);
-            if (Cfg::kDqRounds == 2 && it > 0) dq_send(it - 1, 1);  // second half of the previous partial
+            // ---- statistics of the next tile, then the (rest of the) previous tile's dQ partial; the
+            // barrier inside dq_send (or the explicit one on the first step) publishes the statistics
+            if (it + 1 < n_it) {
+                store_stat(buf ^ 1, stat_next);
+                if (it + 2 < n_it) stat_next = load_stat(i + 2);
+            }
+            if (it == 0) {
+                named_bar_sync(1, kComputeThreads);
+            } else if (Cfg::kDqAliased) {
+                dq_send(it - 1, 1);  // second half of the previous partial
+            } else {
+                dq_fetch(it - 1);
+                dq_send(it - 1, 0);
+            }
         }
 #ifdef B200ATTN_TRACE
         if (tid == 0) BWD_CTA_TRACE(2, b200attn_globaltimer());
