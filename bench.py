@@ -275,6 +275,33 @@ def run_path_kernels(args, B, H, T, d):
     ms_b = timed(lambda c: ops.tiled_causal_attention_backward(q32[0], k32[0], v32[0], o32, merged[0].view(B, H, T, d), m32,
                                                                l32, dq, dk, dv, ws, B, H, T, d, scale))
     fl = flops(B, H, T, d)
+    # interleaved-layout entry points against the chain they replace, BF16 end to end:
+    #   chain: (B,T,3C) -> split -> attention fwd -> merge;  merge^T -> attention bwd -> split^T -> (B,T,3C)
+    iters = max(5, min(args.steps, 50))
+    pq = [ops.fill_normal_(torch.empty(B, T, 3 * H * d, device=dev, dtype=bf16), seed=90 + c) for c in range(copies)]
+    pdo = [ops.fill_normal_(torch.empty(B, T, H * d, device=dev, dtype=bf16), seed=95 + c) for c in range(copies)]
+    pout = [torch.empty(B, T, H * d, device=dev, dtype=bf16) for _ in range(copies)]
+    pdqkv = [torch.empty_like(pq[c]) for c in range(copies)]
+    plse = torch.empty(B, H, T, device=dev)
+    ops.reserve(B * H, T, d)
+
+    def packed_step(c):
+        ops.attention_forward_bf16_packed(pq[c], H, scale, out=pout[c], lse=plse)
+        ops.attention_backward_bf16_packed(pq[c], pout[c], pdo[c], plse, H, scale, dqkv=pdqkv[c])
+
+    def chain_step(c):
+        x = pq[c].view(B, T, 3, H, d).permute(2, 0, 3, 1, 4).contiguous()          # split (one torch copy kernel)
+        o, lse = ops.attention_forward_bf16(x[0], x[1], x[2], scale)
+        pout[c].copy_(o.view(B, H, T, d).permute(0, 2, 1, 3).reshape(B, T, H * d))  # merge
+        do = pdo[c].view(B, T, H, d).permute(0, 2, 1, 3).contiguous()               # merge^T
+        dq_, dk_, dv_ = ops.attention_backward_bf16(x[0], x[1], x[2], o, do, lse, scale)
+        g = pdqkv[c].view(B, T, 3, H, d)                                            # split^T
+        g[:, :, 0].copy_(dq_.view(B, H, T, d).permute(0, 2, 1, 3))
+        g[:, :, 1].copy_(dk_.view(B, H, T, d).permute(0, 2, 1, 3))
+        g[:, :, 2].copy_(dv_.view(B, H, T, d).permute(0, 2, 1, 3))
+
+    ms_packed = timed(packed_step, copies)
+    ms_chain = timed(chain_step, copies)
     print(json.dumps({
         "suite": "path-kernels", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm"], "peak_source": peaks["source"],
         "config": {"workload": workload_name(args, B, H, T, d), "l2": f"{copies} rotating buffer sets"},
@@ -282,6 +309,11 @@ def run_path_kernels(args, B, H, T, d):
         "fp32_parity_mode": {"forward_ms": round(ms_f, 3), "backward_ms": round(ms_b, 3),
                              "tflops": round(fl / ((ms_f + ms_b) * 1e-3) / 1e12, 3),
                              "note": "SIMT FP32, exact expf: the <=1e-5 parity path, not the fast path"},
+        "interleaved_layout": {"packed_fwd_bwd_ms": round(ms_packed, 4), "split_attention_merge_chain_ms": round(ms_chain, 4),
+                               "packed_tflops": round(fl / (ms_packed * 1e-3) / 1e12, 1),
+                               "chain_tflops": round(fl / (ms_chain * 1e-3) / 1e12, 1),
+                               "note": "BF16 (B,T,3C) in, (B,T,C) out and back; the chain uses torch copy kernels for the "
+                                       "four layout passes that b200attn_*_bf16_packed folds into TMA strides"},
     }), flush=True)
 
 

@@ -112,6 +112,20 @@ int b200attn_fwd_bf16(const void* q, const void* k, const void* v, void* out, fl
 /* dq,dk,dv (BH,T,d) bf16, overwritten. Uses library scratch (4*BH*T*d + 8*BH*T bytes). */
 int b200attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* dO, const float* lse,
                       void* dq, void* dk, void* dv, int BH, int T, int d, float scale, b200attn_stream_t stream);
+/* The same kernels on the model's own buffers, with no layout pass on either side: Q, K, V tiles are
+ * fetched straight from the interleaved projection output qkv (B, T, 3*H*d) bf16 (inner order
+ * [Q heads | K heads | V heads], the layout qkv_split_transpose_forward reads,
+ * src/kernels/attention.cu:24-83) through strided tensor maps, and out is stored merged as
+ * (B, T, H*d) bf16 (the layout head_merge_transpose_forward writes, src/kernels/attention.cu:308-345).
+ * Replaces the chain split -> attention -> merge of src/model.cu:305-336. lse is (B*H, T). */
+int b200attn_fwd_bf16_packed(const void* qkv, void* out, float* lse, int B, int T, int H, int d, float scale,
+                             b200attn_stream_t stream);
+/* Backward of the above: dout (B, T, H*d) bf16 in; dqkv (B, T, 3*H*d) bf16 out, overwritten (dK and dV
+ * tiles are stored, and dQ is converted from its FP32 accumulator, directly into their interleaved
+ * places). Replaces head_merge_transpose_backward -> attention backward -> qkv_split_transpose_backward
+ * of src/model.cu:602-653. Uses library scratch like b200attn_bwd_bf16. */
+int b200attn_bwd_bf16_packed(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv, int B,
+                             int T, int H, int d, float scale, b200attn_stream_t stream);
 /* The same backward for callers that must not allocate device memory: hosts whose own pool already
  * owns the whole GPU (a cudaMalloc from a plugin would fail or fragment it), latency-critical loops
  * that cannot take the device-wide synchronisation hidden in cudaMalloc/cudaFree, and sandboxes that

@@ -164,29 +164,28 @@ struct Bump {
     }
 };
 
-// (d, T, BH) BF16 tensor viewed through 64 x 128 x 1 boxes with the 128-byte swizzle.
-int make_map(CUtensorMap* m, const void* base, int BH, int T, int d) {
-    cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
-    cuuint64_t strides[2] = {cuuint64_t(d) * 2, cuuint64_t(T) * d * 2};
-    cuuint32_t box[3] = {64, 128, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (BH=%d T=%d d=%d)", int(r), BH, T, d);
-    return B200ATTN_OK;
-}
+// Element strides of a tensor indexed (b, h, t, e) with e contiguous.
+struct Layout {
+    long long t, h, b;
+};
+Layout slab_layout(int H, int T, int d) { return Layout{d, (long long)T * d, (long long)H * T * d}; }                  // (B, H, T, d)
+Layout packed_qkv_layout(int H, int T, int d) { return Layout{3LL * H * d, d, 3LL * T * H * d}; }                        // (B, T, 3*H*d), one of Q|K|V
+Layout merged_layout(int H, int T, int d) { return Layout{(long long)H * d, d, (long long)T * H * d}; }                // (B, T, H*d)
 
-// (d, T, BH) FP32 tensor viewed through 32 x 128 x 1 boxes (128 bytes per row) with the 128-byte swizzle.
-int make_map_f32(CUtensorMap* m, const void* base, int BH, int T, int d) {
-    cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
-    cuuint64_t strides[2] = {cuuint64_t(d) * 4, cuuint64_t(T) * d * 4};
-    cuuint32_t box[3] = {32, 128, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled (FP32) failed with code %d (BH=%d T=%d d=%d)", int(r), BH, T, d);
+// (d, T, H, B) view of a BF16 (64 x 128 x 1 x 1 boxes) or FP32 (32 x 128 x 1 x 1 boxes: 128 bytes per row) tensor with
+// the 128-byte swizzle. Rows beyond T are zero-filled on load and clipped on store, per (b, h).
+int make_map(CUtensorMap* m, const void* base, bool f32, int B, int H, int T, int d, const Layout& L) {
+    const cuuint64_t es = f32 ? 4 : 2;
+    cuuint64_t dims[4] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(H), cuuint64_t(B)};
+    cuuint64_t strides[3] = {cuuint64_t(L.t) * es, cuuint64_t(L.h) * es, cuuint64_t(L.b) * es};
+    cuuint32_t box[4] = {f32 ? 32u : 64u, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (B=%d H=%d T=%d d=%d, %s)", int(r), B, H, T, d,
+                    f32 ? "FP32" : "BF16");
     return B200ATTN_OK;
 }
 
@@ -206,23 +205,26 @@ int tc_supported(const char* fn, DeviceState* st, int d) {
     return B200ATTN_OK;
 }
 
+// q, k, v share the layout `in_l`; a BF16 output is written through `out_l`, an FP32 output as dense (B*H, T, d).
 int run_fwd_tc(DeviceState* st, const void* q, const void* k, const void* v, void* out, bool out_f32, float* m_out,
-               float* l_out, float* lse_out, int BH, int T, int d, float scale, cudaStream_t stream) {
+               float* l_out, float* lse_out, int B, int H, int T, int d, const Layout& in_l, const Layout& out_l,
+               float scale, cudaStream_t stream) {
     TcFwdArgs a;
     memset(&a, 0, sizeof(a));
+    const int BH = B * H;
     int rc;
-    if ((rc = make_map(&a.map_q, q, BH, T, d))) return rc;
-    if ((rc = make_map(&a.map_k, k, BH, T, d))) return rc;
-    if ((rc = make_map(&a.map_v, v, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_q, q, false, B, H, T, d, in_l))) return rc;
+    if ((rc = make_map(&a.map_k, k, false, B, H, T, d, in_l))) return rc;
+    if ((rc = make_map(&a.map_v, v, false, B, H, T, d, in_l))) return rc;
     if (!out_f32) {
-        if ((rc = make_map(&a.map_o, out, BH, T, d))) return rc;
+        if ((rc = make_map(&a.map_o, out, false, B, H, T, d, out_l))) return rc;
     }
     a.out = out;
     a.out_is_f32 = out_f32 ? 1 : 0;
     a.m_out = m_out;
     a.l_out = l_out;
     a.lse_out = lse_out;
-    a.BH = BH, a.T = T, a.d = d;
+    a.BH = BH, a.T = T, a.d = d, a.H = H;
     a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = st->fault_word;
@@ -231,28 +233,31 @@ int run_fwd_tc(DeviceState* st, const void* q, const void* k, const void* v, voi
     return B200ATTN_OK;
 }
 
+// q, k, v share `in_l`, dO uses `do_l`; BF16 dK/dV are written through `grad_l`, FP32 ones as dense (B*H, T, d);
+// the FP32 dQ accumulator is always dense.
 int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, const void* dO, const float* lse2,
-               const float* D, float* dq_acc, void* dk, void* dv, bool grads_f32, int BH, int T, int d, float scale,
-               cudaStream_t stream) {
+               const float* D, float* dq_acc, void* dk, void* dv, bool grads_f32, int B, int H, int T, int d,
+               const Layout& in_l, const Layout& do_l, const Layout& grad_l, float scale, cudaStream_t stream) {
     TcBwdArgs a;
     memset(&a, 0, sizeof(a));
+    const int BH = B * H;
     int rc;
-    if ((rc = make_map(&a.map_q, q, BH, T, d))) return rc;
-    if ((rc = make_map(&a.map_k, k, BH, T, d))) return rc;
-    if ((rc = make_map(&a.map_v, v, BH, T, d))) return rc;
-    if ((rc = make_map(&a.map_do, dO, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_q, q, false, B, H, T, d, in_l))) return rc;
+    if ((rc = make_map(&a.map_k, k, false, B, H, T, d, in_l))) return rc;
+    if ((rc = make_map(&a.map_v, v, false, B, H, T, d, in_l))) return rc;
+    if ((rc = make_map(&a.map_do, dO, false, B, H, T, d, do_l))) return rc;
     if (!grads_f32) {
-        if ((rc = make_map(&a.map_dk, dk, BH, T, d))) return rc;
-        if ((rc = make_map(&a.map_dv, dv, BH, T, d))) return rc;
+        if ((rc = make_map(&a.map_dk, dk, false, B, H, T, d, grad_l))) return rc;
+        if ((rc = make_map(&a.map_dv, dv, false, B, H, T, d, grad_l))) return rc;
     }
-    if ((rc = make_map_f32(&a.map_dq_acc, dq_acc, BH, T, d))) return rc;
+    if ((rc = make_map(&a.map_dq_acc, dq_acc, true, B, H, T, d, slab_layout(H, T, d)))) return rc;
     a.lse2 = lse2;
     a.D = D;
     a.dq_acc = dq_acc;
     a.dk = dk;
     a.dv = dv;
     a.grads_are_f32 = grads_f32 ? 1 : 0;
-    a.BH = BH, a.T = T, a.d = d;
+    a.BH = BH, a.T = T, a.d = d, a.H = H;
     a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = st->fault_word;
@@ -416,7 +421,8 @@ extern "C" int b200attn_fwd_f32(const float* q, const float* k, const float* v, 
     RETURN_IF_CUDA(launch_f32_to_bf16(q, qb, (long long)n, stream), "convert q");
     RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
     RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
-    return run_fwd_tc(st, qb, kb, vb, out, true, m_out, l_out, nullptr, BH, T, d, scale, stream);
+    const Layout sl = slab_layout(BH, T, d);
+    return run_fwd_tc(st, qb, kb, vb, out, true, m_out, l_out, nullptr, 1, BH, T, d, sl, sl, scale, stream);
 }
 
 extern "C" int b200attn_dot_do_o_f32(const float* dO, const float* O, float* D, int B, int H, int T, int d,
@@ -483,7 +489,8 @@ extern "C" int b200attn_bwd_f32(const float* q, const float* k, const float* v, 
     // dq is the FP32 accumulator itself: partial sums are reduced straight into the caller's buffer,
     // which the pre-pass clears
     RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, dq, rows, d, stream), "pre-pass");
-    return run_bwd_tc(st, qb, kb, vb, dob, lse2, workspace, dq, dk, dv, true, BH, T, d, scale, stream);
+    const Layout sl = slab_layout(BH, T, d);
+    return run_bwd_tc(st, qb, kb, vb, dob, lse2, workspace, dq, dk, dv, true, 1, BH, T, d, sl, sl, sl, scale, stream);
 }
 
 extern "C" int b200attn_merge_heads_f32(const float* in, float* out, int B, int H, int T, int d,
@@ -522,7 +529,8 @@ extern "C" int b200attn_fwd_bf16(const void* q, const void* k, const void* v, vo
     DeviceState* st = nullptr;
     if ((rc = device_state(stream, &st))) return rc;
     if ((rc = tc_supported(fn, st, d))) return rc;
-    return run_fwd_tc(st, q, k, v, out, false, nullptr, nullptr, lse, BH, T, d, scale, stream);
+    const Layout sl = slab_layout(BH, T, d);
+    return run_fwd_tc(st, q, k, v, out, false, nullptr, nullptr, lse, 1, BH, T, d, sl, sl, scale, stream);
 }
 
 extern "C" int b200attn_bwd_bf16(const void* q, const void* k, const void* v, const void* o, const void* dO,
@@ -551,8 +559,64 @@ extern "C" int b200attn_bwd_bf16(const void* q, const void* k, const void* v, co
     const __nv_bfloat16* ob = static_cast<const __nv_bfloat16*>(o);
     const __nv_bfloat16* dob = static_cast<const __nv_bfloat16*>(dO);
     RETURN_IF_CUDA(launch_bwd_prepass<__nv_bfloat16>(ob, dob, nullptr, nullptr, lse, D, lse2, dq_acc, rows, d, stream), "pre-pass");
-    if ((rc = run_bwd_tc(st, q, k, v, dO, lse2, D, dq_acc, dk, dv, false, BH, T, d, scale, stream))) return rc;
+    const Layout sl = slab_layout(BH, T, d);
+    if ((rc = run_bwd_tc(st, q, k, v, dO, lse2, D, dq_acc, dk, dv, false, 1, BH, T, d, sl, sl, sl, scale, stream))) return rc;
     RETURN_IF_CUDA(launch_dq_convert(dq_acc, static_cast<__nv_bfloat16*>(dq), (long long)n, stream), "dq convert");
+    return B200ATTN_OK;
+}
+
+// ---------------------------------------------------------------------- interleaved layouts
+// The same kernels on the model's own buffers: Q, K, V tiles are fetched straight from the (B, T, 3*H*d)
+// projection output and O is stored merged as (B, T, H*d), through strided tensor maps; no split / merge pass.
+extern "C" int b200attn_fwd_bf16_packed(const void* qkv, void* out, float* lse, int B, int T, int H, int d, float scale,
+                                        b200attn_stream_t stream_) {
+    const char* fn = "b200attn_fwd_bf16_packed";
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    if ((long long)B * H * T == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, qkv); REQUIRE_PTR(fn, out); REQUIRE_PTR(fn, lse);
+    if (!aligned16(qkv) || !aligned16(out)) return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", fn);
+    DeviceState* st = nullptr;
+    if ((rc = device_state(stream, &st))) return rc;
+    if ((rc = tc_supported(fn, st, d))) return rc;
+    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(qkv);
+    const size_t C = size_t(H) * d;
+    return run_fwd_tc(st, base, base + C, base + 2 * C, out, false, nullptr, nullptr, lse, B, H, T, d,
+                      packed_qkv_layout(H, T, d), merged_layout(H, T, d), scale, stream);
+}
+
+extern "C" int b200attn_bwd_bf16_packed(const void* qkv, const void* out, const void* dout, const float* lse, void* dqkv,
+                                        int B, int T, int H, int d, float scale, b200attn_stream_t stream_) {
+    const char* fn = "b200attn_bwd_bf16_packed";
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int rc = check_dims4(fn, B, H, T, d);
+    if (rc) return rc;
+    const long long rows = (long long)B * H * T;
+    if (rows == 0) return B200ATTN_OK;
+    REQUIRE_PTR(fn, qkv); REQUIRE_PTR(fn, out); REQUIRE_PTR(fn, dout); REQUIRE_PTR(fn, lse); REQUIRE_PTR(fn, dqkv);
+    if (!aligned16(qkv) || !aligned16(out) || !aligned16(dout) || !aligned16(dqkv))
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", fn);
+    DeviceState* st = nullptr;
+    if ((rc = device_state(stream, &st))) return rc;
+    if ((rc = tc_supported(fn, st, d))) return rc;
+    const int BH = B * H;
+    const size_t n = size_t(rows) * d;
+    if ((rc = ensure_scratch(st, scratch_for(BH, T, d), stream))) return rc;
+    Bump bump{st->scratch};
+    float* dq_acc = bump.take<float>(n);
+    float* D = bump.take<float>(size_t(rows));
+    float* lse2 = bump.take<float>(size_t(rows));
+    const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(qkv);
+    __nv_bfloat16* gb = static_cast<__nv_bfloat16*>(dqkv);
+    const size_t C = size_t(H) * d;
+    const Layout pl = packed_qkv_layout(H, T, d), ml = merged_layout(H, T, d);
+    RETURN_IF_CUDA(launch_bwd_prepass_strided(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout),
+                                              lse, D, lse2, dq_acc, rows, d, T, H, ml.t, ml.h, ml.b, stream), "pre-pass");
+    if ((rc = run_bwd_tc(st, qb, qb + C, qb + 2 * C, dout, lse2, D, dq_acc, gb + C, gb + 2 * C, false, B, H, T, d, pl, ml, pl,
+                         scale, stream)))
+        return rc;
+    RETURN_IF_CUDA(launch_dq_convert_strided(dq_acc, gb, rows, d, T, H, pl.t, pl.h, pl.b, stream), "dq convert");
     return B200ATTN_OK;
 }
 

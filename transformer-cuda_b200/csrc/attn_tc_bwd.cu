@@ -128,6 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     // so that the CTAs resident at one time share few slabs and their tiles stay in L2.
     const int bh = a.tile_major_order ? int(blockIdx.x % a.BH) : int(blockIdx.x / n_tiles);
     const int jt = a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_tiles);
+    const int hh = bh % a.H, bb = bh / a.H;  // head and batch coordinates of the 4-D tensor maps
     const int n_it = n_tiles - jt;        // query tiles jt .. n_tiles-1
 #ifdef B200ATTN_TRACE
     if (threadIdx.x == 0) {
@@ -176,10 +177,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             tma_prefetch_desc(&a.map_do);
             mbar_expect_tx(&bars.k_full, Cfg::kTileBytes);
             for (int at = 0; at < Cfg::kAtoms; ++at)
-                tma_load_3d(sK + at * kAtomBytes, &a.map_k, &bars.k_full, at * 64, jt * kBKV, bh);
+                tma_load_4d(sK + at * kAtomBytes, &a.map_k, &bars.k_full, at * 64, jt * kBKV, hh, bb);
             mbar_expect_tx(&bars.v_full, Cfg::kTileBytes);
             for (int at = 0; at < Cfg::kAtoms; ++at)
-                tma_load_3d(sV + at * kAtomBytes, &a.map_v, &bars.v_full, at * 64, jt * kBKV, bh);
+                tma_load_4d(sV + at * kAtomBytes, &a.map_v, &bars.v_full, at * 64, jt * kBKV, hh, bb);
             for (int it = 0; it < n_it; ++it) {
                 const int i = jt + it;
                 const int qs = it % Cfg::kQStages;
@@ -187,13 +188,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     mbar_wait(&bars.q_empty[qs], (it / Cfg::kQStages - 1) & 1, &abort_flag, a.fault_word, 0x40);
                 mbar_expect_tx(&bars.q_full[qs], Cfg::kTileBytes);
                 for (int at = 0; at < Cfg::kAtoms; ++at)
-                    tma_load_3d(sQ + qs * Cfg::kTileBytes + at * kAtomBytes, &a.map_q, &bars.q_full[qs], at * 64, i * kBQ, bh);
+                    tma_load_4d(sQ + qs * Cfg::kTileBytes + at * kAtomBytes, &a.map_q, &bars.q_full[qs], at * 64, i * kBQ, hh, bb);
                 const int os = it % Cfg::kDoStages;
                 if (it >= Cfg::kDoStages)
                     mbar_wait(&bars.do_empty[os], (it / Cfg::kDoStages - 1) & 1, &abort_flag, a.fault_word, 0x41);
                 mbar_expect_tx(&bars.do_full[os], Cfg::kTileBytes);
                 for (int at = 0; at < Cfg::kAtoms; ++at)
-                    tma_load_3d(sDO + os * Cfg::kTileBytes + at * kAtomBytes, &a.map_do, &bars.do_full[os], at * 64, i * kBQ, bh);
+                    tma_load_4d(sDO + os * Cfg::kTileBytes + at * kAtomBytes, &a.map_do, &bars.do_full[os], at * 64, i * kBQ, hh, bb);
             }
         }
         __syncwarp();
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 for (int kk = 0; kk < kBQ / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kAtomBytes + (kk & 3) * 32;
                     tc_mma_ss(tmem + Cfg::kColDK, desc_advance(ds_kmaj, off), desc_advance(q_mnmaj, kk * 2048), idesc_kv,
-                              (it > 0) || (kk > 0));
+                                  (it > 0) || (kk > 0));
                 }
                 tc_commit(&bars.q_empty[qs]);  // S^T(it) and dK(it) were the readers of this Q tile
             }
@@ -327,20 +328,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             mbar_arrive(&bars.dq_empty);
         };
         auto dq_send = [&](int it, int rd) {  // registers -> staging -> reduce-add, 32 columns per thread
-#ifdef B200ATTN_DQ_RED
-            {   // experiment: vector reductions straight from registers, no staging
-                const int q_row = (jt + it) * kBQ + r;
-                if (q_row < a.T) {
-                    float* dst = a.dq_acc + ((long long)bh * a.T + q_row) * D + half * (D / 2) + rd * 32;
-#pragma unroll
-                    for (int x = 0; x < 32; x += 4)
-                        red_add_v4(dst + x, __uint_as_float(dqv[rd * 32 + x]), __uint_as_float(dqv[rd * 32 + x + 1]),
-                                   __uint_as_float(dqv[rd * 32 + x + 2]), __uint_as_float(dqv[rd * 32 + x + 3]));
-                }
-                named_bar_sync(2, kComputeThreads);
-                return;
-            }
-#endif
             if (tid == 0) tma_store_wait_read();  // earlier reductions have finished reading the staging tile
             named_bar_sync(2, kComputeThreads);
             if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 13);
@@ -353,8 +340,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             named_bar_sync(2, kComputeThreads);
             if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 14);
             if (tid == 0) {
-                tma_reduce_add_3d(&a.map_dq_acc, sDQ, rd * 32, (jt + it) * kBQ, bh);
-                tma_reduce_add_3d(&a.map_dq_acc, sDQ + kAtomBytes, D / 2 + rd * 32, (jt + it) * kBQ, bh);
+                tma_reduce_add_4d(&a.map_dq_acc, sDQ, rd * 32, (jt + it) * kBQ, hh, bb);
+                tma_reduce_add_4d(&a.map_dq_acc, sDQ + kAtomBytes, D / 2 + rd * 32, (jt + it) * kBQ, hh, bb);
                 tma_store_commit();
             }
         };
@@ -536,8 +523,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             named_bar_sync(1, kComputeThreads);
             if (tid == 0) {
                 for (int at = 0; at < Cfg::kAtoms; ++at) {
-                    tma_store_3d(&a.map_dv, sQ + at * kAtomBytes, at * 64, jt * kBKV, bh);
-                    tma_store_3d(&a.map_dk, sQ + Cfg::kTileBytes + at * kAtomBytes, at * 64, jt * kBKV, bh);
+                    tma_store_4d(&a.map_dv, sQ + at * kAtomBytes, at * 64, jt * kBKV, hh, bb);
+                    tma_store_4d(&a.map_dk, sQ + Cfg::kTileBytes + at * kAtomBytes, at * 64, jt * kBKV, hh, bb);
                 }
                 tma_store_commit();
             }
@@ -599,6 +586,61 @@ __global__ void __launch_bounds__(256) bwd_prepass_kernel(const TIn* __restrict_
     }
 }
 
+// Pre-pass on BF16 O / dO whose rows are addressed through strides (merged (B, T, H*d) layout): eight threads per
+// 64-wide row (sixteen per 128), 16 bytes each. D, lse2 and the dQ accumulator stay dense (B*H, T[, d]).
+__global__ void __launch_bounds__(256) bwd_prepass_strided_kernel(const __nv_bfloat16* __restrict__ o,
+                                                                 const __nv_bfloat16* __restrict__ dO,
+                                                                 const float* __restrict__ lse, float* __restrict__ Dout,
+                                                                 float* __restrict__ lse2, float* __restrict__ zero,
+                                                                 long long rows, int d, int T, int H, long long lt,
+                                                                 long long lh, long long lb) {
+    const int tpr = d / 8;
+    const long long gid = blockIdx.x * 256ll + threadIdx.x;
+    const long long row = gid / tpr;
+    const int e = int(gid % tpr) * 8;
+    float acc = 0.f;
+    if (row < rows) {
+        const long long bh = row / T;
+        const int t = int(row - bh * T);
+        const long long src = (bh / H) * lb + (bh % H) * lh + (long long)t * lt + e;
+        const uint4 ua = __ldg(reinterpret_cast<const uint4*>(o + src));
+        const uint4 ub = __ldg(reinterpret_cast<const uint4*>(dO + src));
+        const __nv_bfloat16* pa = reinterpret_cast<const __nv_bfloat16*>(&ua);
+        const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&ub);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) acc = fmaf(__bfloat162float(pa[x]), __bfloat162float(pb[x]), acc);
+        float4* z = reinterpret_cast<float4*>(zero + row * d + e);
+        z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (row < rows && e == 0) {
+        Dout[row] = acc;
+        lse2[row] = lse[row] * kLog2e;
+    }
+}
+
+// dQ accumulator (dense FP32 rows) -> BF16 rows addressed through strides; one thread per 8 elements.
+__global__ void __launch_bounds__(256) dq_convert_strided_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                                long long rows, int d, int T, int H, long long lt,
+                                                                long long lh, long long lb) {
+    const int tpr = d / 8;
+    const long long gid = blockIdx.x * 256ll + threadIdx.x;
+    const long long row = gid / tpr;
+    const int e = int(gid % tpr) * 8;
+    if (row >= rows) return;
+    const long long bh = row / T;
+    const int t = int(row - bh * T);
+    const float4 a0 = __ldg(reinterpret_cast<const float4*>(acc + row * d + e));
+    const float4 a1 = __ldg(reinterpret_cast<const float4*>(acc + row * d + e + 4));
+    uint4 w;
+    w.x = pack_bf16x2(a0.x, a0.y);
+    w.y = pack_bf16x2(a0.z, a0.w);
+    w.z = pack_bf16x2(a1.x, a1.y);
+    w.w = pack_bf16x2(a1.z, a1.w);
+    *reinterpret_cast<uint4*>(dq + (bh / H) * lb + (bh % H) * lh + (long long)t * lt + e) = w;
+}
+
 template <int D, bool GRADS_F32>
 cudaError_t launch_bwd(const TcBwdArgs& a, cudaStream_t stream) {
     using Cfg = BwdCfg<D>;
@@ -636,6 +678,27 @@ template cudaError_t launch_bwd_prepass<float>(const float*, const float*, const
 template cudaError_t launch_bwd_prepass<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const float*,
                                                       const float*, const float*, float*, float*, float*, long long,
                                                       int, cudaStream_t);
+
+cudaError_t launch_bwd_prepass_strided(const __nv_bfloat16* o, const __nv_bfloat16* dO, const float* lse, float* D,
+                                       float* lse2, float* zero, long long rows, int d, int T, int H, long long lt,
+                                       long long lh, long long lb, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const int tpr = d / 8;
+    if (d % 8 != 0 || tpr > 32 || (tpr & (tpr - 1)) != 0 || !lse || !lse2 || !zero) return cudaErrorInvalidValue;
+    const long long threads = rows * tpr;
+    bwd_prepass_strided_kernel<<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(o, dO, lse, D, lse2, zero, rows, d, T,
+                                                                                         H, lt, lh, lb);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, long long rows, int d, int T, int H,
+                                      long long lt, long long lh, long long lb, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    if (d % 8 != 0) return cudaErrorInvalidValue;
+    const long long threads = rows * (d / 8);
+    dq_convert_strided_kernel<<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(dq_acc, dq, rows, d, T, H, lt, lh, lb);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {
     return launch_f32_to_bf16(dq_acc, dq, n, stream);

@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
     // problem fits in L2 (shortest tail), else slab by slab (resident CTAs share K/V tiles in L2).
     const int bh = a.tile_major_order ? int(blockIdx.x % a.BH) : int(blockIdx.x / n_q_tiles);
     const int qt = n_q_tiles - 1 - (a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_q_tiles));
+    const int hh = bh % a.H, bb = bh / a.H;  // head and batch coordinates of the 4-D tensor maps
     const int n_kv = qt + 1;                                  // key tiles 0..qt; qt is the diagonal tile
 
     if (tid == 0) {
@@ -136,18 +137,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             tma_prefetch_desc(&a.map_v);
             mbar_expect_tx(&bars.q_full, Cfg::kTileBytes);
             for (int at = 0; at < Cfg::kAtoms; ++at)
-                tma_load_3d(sQ + at * kAtomBytes, &a.map_q, &bars.q_full, at * 64, qt * kBM, bh);
+                tma_load_4d(sQ + at * kAtomBytes, &a.map_q, &bars.q_full, at * 64, qt * kBM, hh, bb);
             for (int j = 0; j < n_kv; ++j) {
                 const int ks = j % Cfg::kKStages, kround = j / Cfg::kKStages;
                 if (kround > 0) mbar_wait(&bars.k_empty[ks], (kround - 1) & 1, &abort_flag, a.fault_word, 0x10);
                 mbar_expect_tx(&bars.k_full[ks], Cfg::kTileBytes);
                 for (int at = 0; at < Cfg::kAtoms; ++at)
-                    tma_load_3d(sK + ks * Cfg::kTileBytes + at * kAtomBytes, &a.map_k, &bars.k_full[ks], at * 64, j * kBN, bh);
+                    tma_load_4d(sK + ks * Cfg::kTileBytes + at * kAtomBytes, &a.map_k, &bars.k_full[ks], at * 64, j * kBN, hh, bb);
                 const int vs = j % Cfg::kVStages, vround = j / Cfg::kVStages;
                 if (vround > 0) mbar_wait(&bars.v_empty[vs], (vround - 1) & 1, &abort_flag, a.fault_word, 0x11);
                 mbar_expect_tx(&bars.v_full[vs], Cfg::kTileBytes);
                 for (int at = 0; at < Cfg::kAtoms; ++at)
-                    tma_load_3d(sV + vs * Cfg::kTileBytes + at * kAtomBytes, &a.map_v, &bars.v_full[vs], at * 64, j * kBN, bh);
+                    tma_load_4d(sV + vs * Cfg::kTileBytes + at * kAtomBytes, &a.map_v, &bars.v_full[vs], at * 64, j * kBN, hh, bb);
             }
         }
         __syncwarp();
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             fence_proxy_async_smem();
             named_bar_sync(1, kSoftmaxThreads);
             if (tid == 0) {
-                for (int at = 0; at < Cfg::kAtoms; ++at) tma_store_3d(&a.map_o, sQ + at * kAtomBytes, at * 64, qt * kBM, bh);
+                for (int at = 0; at < Cfg::kAtoms; ++at) tma_store_4d(&a.map_o, sQ + at * kAtomBytes, at * 64, qt * kBM, hh, bb);
                 tma_store_commit();
                 tma_store_wait_read();  // the staging tile must outlive the bulk read; the write completes with the grid
             }

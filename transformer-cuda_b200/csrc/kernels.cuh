@@ -51,14 +51,17 @@ cudaError_t launch_attn_bwd_f32_tiled(const float* q, const float* k, const floa
                                       int d, float scale, cudaStream_t stream);
 
 // ------------------------------------------------------------------ attn_tc_fwd.cu / attn_tc_bwd.cu (tcgen05)
+// Tensor maps are 4-D (d, T, H, B) with free T / H / B strides, box 64 x 128 x 1 x 1 (FP32: 32 x 128 x 1 x 1) and the
+// 128-byte swizzle; slab bh = b*H + h. (B, H, T, d) slabs and the interleaved (B, T, 3*H*d) buffer differ only in strides.
 struct TcFwdArgs {
-    CUtensorMap map_q, map_k, map_v, map_o;  // (d, T, BH) BF16 tensors, box 64 x 128 x 1, 128-byte swizzle
+    CUtensorMap map_q, map_k, map_v, map_o;  // BF16
     void* out;                               // BF16 or FP32 (BH, T, d), selected by out_is_f32
     int out_is_f32;
     float* m_out;                            // optional (BH, T): row max of scaled scores
     float* l_out;                            // optional (BH, T): sum exp(s - m)
     float* lse_out;                          // optional (BH, T): m + log(l)
     int BH, T, d;
+    int H;                 // heads per batch entry of the maps (BH % H == 0); statistics stay (BH, T)
     int tile_major_order;  // 1: CTAs ordered longest tile first across all slabs; 0: slab by slab
     float scale;
     unsigned int* fault_word;
@@ -67,9 +70,9 @@ cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream);        
 cudaError_t launch_attn_fwd_tc_short(const TcFwdArgs& a, cudaStream_t stream);  // two CTAs per SM, T <= 2048
 
 struct TcBwdArgs {
-    CUtensorMap map_q, map_k, map_v, map_do;  // BF16 (d, T, BH)
+    CUtensorMap map_q, map_k, map_v, map_do;  // BF16
     CUtensorMap map_dk, map_dv;               // BF16 outputs (used when grads_are_f32 == 0)
-    CUtensorMap map_dq_acc;                   // FP32 (d, T, BH) view of dq_acc, box 32 x 128 x 1, 128-byte swizzle
+    CUtensorMap map_dq_acc;                   // FP32 view of dq_acc (always dense (BH, T, d))
     const float* lse2;                        // (BH, T) log-sum-exp in log2 units: lse * log2(e)
     const float* D;                           // (BH, T) rowsum(dO * O)
     float* dq_acc;                            // (BH, T, d) FP32, zeroed before launch, receives sum of partials
@@ -77,6 +80,7 @@ struct TcBwdArgs {
     void* dv;
     int grads_are_f32;
     int BH, T, d;
+    int H;                 // heads per batch entry of the maps (BH % H == 0)
     int tile_major_order;  // 1: CTAs ordered longest tile first across all slabs; 0: slab by slab
     float scale;
     unsigned int* fault_word;
@@ -90,6 +94,13 @@ cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream);
 template <typename TIn>
 cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse,
                                float* D, float* lse2, float* zero, long long rows, int d, cudaStream_t stream);
+// The same for BF16 O / dO rows addressed as base + b*lb + h*lh + t*lt (+ e), row = (b*H + h)*T + t; lse given.
+cudaError_t launch_bwd_prepass_strided(const __nv_bfloat16* o, const __nv_bfloat16* dO, const float* lse, float* D,
+                                       float* lse2, float* zero, long long rows, int d, int T, int H, long long lt,
+                                       long long lh, long long lb, cudaStream_t stream);
+// dq (BF16, rows addressed as above) = dq_acc (FP32, dense rows).
+cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, long long rows, int d, int T, int H,
+                                      long long lt, long long lh, long long lb, cudaStream_t stream);
 // dq (BF16) = dq_acc (FP32), elementwise.
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 

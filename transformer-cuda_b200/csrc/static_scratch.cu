@@ -96,14 +96,15 @@ int setup_current_device(PerDevice** out) {
     return B200ATTN_OK;
 }
 
-// BF16 tensors: 64 x 128 x 1 boxes; the FP32 dQ accumulator: 32 x 128 x 1 boxes (both 128 bytes per row).
+// Dense (BH, T, d) tensors as the 4-D (d, T, H = BH, B = 1) maps the kernels take. BF16: 64 x 128 x 1 x 1 boxes;
+// the FP32 dQ accumulator: 32 x 128 x 1 x 1 boxes (both 128 bytes per row).
 int encode_map(CUtensorMap* m, const void* base, int BH, int T, int d, bool f32 = false) {
     const cuuint64_t esz = f32 ? 4 : 2;
-    cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH)};
-    cuuint64_t strides[2] = {cuuint64_t(d) * esz, cuuint64_t(T) * d * esz};
-    cuuint32_t box[3] = {f32 ? 32u : 64u, 128, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_encode_fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+    cuuint64_t dims[4] = {cuuint64_t(d), cuuint64_t(T), cuuint64_t(BH), 1};
+    cuuint64_t strides[3] = {cuuint64_t(d) * esz, cuuint64_t(T) * d * esz, cuuint64_t(BH) * T * d * esz};
+    cuuint32_t box[4] = {f32 ? 32u : 64u, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode_fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                              const_cast<void*>(base), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -162,7 +163,7 @@ extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const voi
     a.dk = dk;
     a.dv = dv;
     a.grads_are_f32 = 0;
-    a.BH = BH, a.T = T, a.d = d;
+    a.BH = BH, a.T = T, a.d = d, a.H = BH;
     a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = fault_word;

@@ -47,6 +47,8 @@ _SIGNATURES = {
     "b200attn_fwd_bf16": ([_P, _P, _P, _P, _P, _I, _I, _I, _F, _P], _I),
     "b200attn_bwd_bf16": ([_P] * 9 + [_I, _I, _I, _F, _P], _I),
     "b200attn_bwd_bf16_noalloc": ([_P] * 9 + [_I, _I, _I, _F, _P], _I),
+    "b200attn_fwd_bf16_packed": ([_P] * 3 + [_I, _I, _I, _I, _F, _P], _I),
+    "b200attn_bwd_bf16_packed": ([_P] * 5 + [_I, _I, _I, _I, _F, _P], _I),
     "b200attn_qkv_split_bf16": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_qkv_merge_grad_bf16": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_merge_heads_bf16": ([_P, _P, _I, _I, _I, _I, _P], _I),

@@ -153,6 +153,28 @@ def attention_backward_bf16_noalloc(q, k, v, o, dO, lse, scale, dq, dk, dv):
     return dq, dk, dv
 
 
+def attention_forward_bf16_packed(qkv, H, scale, out=None, lse=None):
+    """Attention straight on the projection output: qkv BF16 (B, T, 3*H*d) with inner order
+    [Q heads | K heads | V heads]; returns (out BF16 (B, T, H*d), lse FP32 (B, H, T)). No split or merge pass."""
+    B, T, C3 = qkv.shape
+    d = C3 // (3 * H)
+    out = torch.empty(B, T, H * d, device=qkv.device, dtype=BF16) if out is None else out
+    lse = torch.empty(B, H, T, device=qkv.device, dtype=F32) if lse is None else lse
+    _lib.call("b200attn_fwd_bf16_packed", _ptr(qkv, BF16, "qkv"), _ptr(out, BF16, "out"), _ptr(lse, F32, "lse"),
+              B, T, H, d, float(scale), _stream())
+    return out, lse
+
+
+def attention_backward_bf16_packed(qkv, out, dout, lse, H, scale, dqkv=None):
+    """Backward of attention_forward_bf16_packed: dout BF16 (B, T, H*d) -> dqkv BF16 (B, T, 3*H*d), overwritten."""
+    B, T, C3 = qkv.shape
+    d = C3 // (3 * H)
+    dqkv = torch.empty_like(qkv) if dqkv is None else dqkv
+    _lib.call("b200attn_bwd_bf16_packed", _ptr(qkv, BF16, "qkv"), _ptr(out, BF16, "out"), _ptr(dout, BF16, "dout"),
+              _ptr(lse, F32, "lse"), _ptr(dqkv, BF16, "dqkv"), B, T, H, d, float(scale), _stream())
+    return dqkv
+
+
 def qkv_split_transpose_forward_bf16(qkv, q, k, v, B, T, H, d_head):
     """FP32 (B,T,3*H*d) -> BF16 q,k,v (B,H,T,d)."""
     _lib.call("b200attn_qkv_split_bf16", _ptr(qkv, F32, "qkv"), _ptr(q, BF16, "q"), _ptr(k, BF16, "k"),
