@@ -331,6 +331,9 @@ def main():
                     help="c2 (default), c3, c5_*: the attention path; c4: the data-parallel GPT training step around it")
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-event-stride", type=int, default=32,
+                    help="bracket every N-th launch of each tensor-core kernel with CUDA events inside the timed region "
+                         "(roofline durations); events between kernels undo their back-to-back launch, so N=1 slows the step")
     ap.add_argument("--suite", default="attention", choices=["attention", "path-kernels"],
                     help="'path-kernels': time every other launcher of the path (layout, softmax, pre-pass, FP32 parity "
                          "kernels) against the HBM roofline and print one JSON line with a table")
@@ -396,7 +399,7 @@ def main():
         sampler.wait_first_sample()
 
     # ---- device-timed region: exactly K steps between barrier + synchronize on both sides
-    ops.kernel_timing(True)
+    ops.kernel_timing(True, every=args.kernel_event_stride)
     pdist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -496,6 +499,8 @@ def main():
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_tc_kernel", "achieved": bwd_tf, "peak": peaks["bf16"],
                      "unit": UNIT, "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} (burst cuBLAS BF16)",
                      "traffic": ncu_traffic_per_launch(args.workload), "launch_ms": bwd_ms,
+                     "timed_launches": kt["bwd_launches"],
+                     "timing": f"CUDA events around every {args.kernel_event_stride}-th launch inside the timed region",
                      "flops_per_launch": 5.0 * BH * T * T * d,
                      "forward_kernel": {"kernel": "attn_fwd_tc_kernel", "achieved": fwd_tf, "launch_ms": fwd_ms,
                                         "frac": fwd_tf / peaks["bf16"]}},

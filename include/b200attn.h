@@ -51,9 +51,11 @@ int b200attn_release(void);
  * waits ran out (0 = none); clears the word. `code` is a HOST pointer and may be NULL. */
 int b200attn_check_device_fault(unsigned int* code);
 
-/* Per-launch timing of the two tensor-core kernels, for roofline reporting: while enabled, every
- * launch of the forward / backward tcgen05 kernel is bracketed by CUDA events on its stream
- * (not to be enabled while capturing a graph). Enabling or disabling clears earlier records.
+/* Per-launch timing of the two tensor-core kernels, for roofline reporting: with enable = N > 0,
+ * every N-th launch of the forward / backward tcgen05 kernel is bracketed by CUDA events on its
+ * stream (N = 1: every launch; an event record between two kernels undoes their programmatic
+ * back-to-back launch, so N > 1 leaves most steps undisturbed; not to be enabled while capturing
+ * a graph). Enabling (any N) or disabling (0) clears earlier records.
  * b200attn_kernel_times waits for the recorded launches and returns the summed durations in
  * milliseconds and the launch counts (HOST pointers, any may be NULL). No reference counterpart:
  * the reference times whole phases with its GpuTimer (include/common.h:35-62). */

@@ -61,6 +61,7 @@ struct TimedLaunch {
     int kind;  // 0 forward kernel, 1 backward kernel
 };
 std::atomic<int> g_timing_enabled{0};
+std::atomic<int> g_timing_counter[2];
 std::vector<TimedLaunch> g_timed;
 std::mutex g_timed_mutex;
 
@@ -69,7 +70,11 @@ struct ScopedKernelTimer {
     TimedLaunch t{};
     bool active = false;
     ScopedKernelTimer(int kind, cudaStream_t s) : stream(s) {
-        if (!g_timing_enabled.load()) return;
+        const int stride = g_timing_enabled.load();
+        if (stride <= 0) return;
+        // every stride-th launch of a kind is bracketed by events; the others keep their back-to-back
+        // (programmatically serialised) launch, which an event record in between would undo
+        if (g_timing_counter[kind & 1].fetch_add(1) % stride != 0) return;
         if (cudaEventCreate(&t.start) != cudaSuccess || cudaEventCreate(&t.stop) != cudaSuccess) return;
         t.kind = kind;
         active = cudaEventRecord(t.start, stream) == cudaSuccess;
@@ -324,7 +329,9 @@ extern "C" int b200attn_kernel_timing(int enable) {
         cudaEventDestroy(t.stop);
     }
     g_timed.clear();
-    g_timing_enabled.store(enable ? 1 : 0);
+    g_timing_counter[0].store(0);
+    g_timing_counter[1].store(0);
+    g_timing_enabled.store(enable > 0 ? enable : 0);
     return B200ATTN_OK;
 }
 

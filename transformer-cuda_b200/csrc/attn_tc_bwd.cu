@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    pdl_launch_dependents();
 
     const int n_tiles = (a.T + kBKV - 1) / kBKV;
     // CTA order. Key tile 0 sees every query tile and is the longest. When the whole problem fits in
@@ -167,6 +168,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
+    // barriers, TMEM and the tensor maps are set up: from here on global memory is touched, so wait for the
+    // kernel in front of this one in the stream (returns at once for an ordinary launch)
+    pdl_wait();
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
@@ -561,6 +565,8 @@ __global__ void __launch_bounds__(256) bwd_prepass_kernel(const TIn* __restrict_
                                                          float* __restrict__ lse2, float* __restrict__ zero,
                                                          long long rows, int d) {
     constexpr int VEC = 16 / sizeof(TIn);
+    pdl_launch_dependents();
+    pdl_wait();
     const int tpr = d / VEC;  // threads per row: a power of two <= 32
     const long long gid = blockIdx.x * 256ll + threadIdx.x;
     const long long row = gid / tpr;
@@ -594,6 +600,8 @@ __global__ void __launch_bounds__(256) bwd_prepass_strided_kernel(const __nv_bfl
                                                                  float* __restrict__ lse2, float* __restrict__ zero,
                                                                  long long rows, int d, int T, int H, long long lt,
                                                                  long long lh, long long lb) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int tpr = d / 8;
     const long long gid = blockIdx.x * 256ll + threadIdx.x;
     const long long row = gid / tpr;
@@ -624,6 +632,8 @@ __global__ void __launch_bounds__(256) bwd_prepass_strided_kernel(const __nv_bfl
 __global__ void __launch_bounds__(256) dq_convert_strided_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
                                                                 long long rows, int d, int T, int H, long long lt,
                                                                 long long lh, long long lb) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int tpr = d / 8;
     const long long gid = blockIdx.x * 256ll + threadIdx.x;
     const long long row = gid / tpr;
@@ -649,8 +659,7 @@ cudaError_t launch_bwd(const TcBwdArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const int n_tiles = (a.T + kBKV - 1) / kBKV;
     const long long blocks = (long long)n_tiles * a.BH;
-    kern<<<(unsigned int)blocks, kThreads, Cfg::kSmemBytes, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, dim3((unsigned int)blocks), dim3(kThreads), Cfg::kSmemBytes, stream, a);
 }
 
 }  // namespace
@@ -670,8 +679,8 @@ cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, cons
     const int tpr = d / VEC;
     if (d % VEC != 0 || tpr > 32 || (tpr & (tpr - 1)) != 0) return cudaErrorInvalidValue;
     const long long threads = rows * tpr;
-    bwd_prepass_kernel<TIn><<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(o, dO, m, l, lse, D, lse2, zero, rows, d);
-    return cudaGetLastError();
+    return launch_pdl(bwd_prepass_kernel<TIn>, dim3((unsigned int)((threads + 255) / 256)), dim3(256), 0, stream, o, dO, m, l, lse,
+                      D, lse2, zero, rows, d);
 }
 template cudaError_t launch_bwd_prepass<float>(const float*, const float*, const float*, const float*, const float*,
                                               float*, float*, float*, long long, int, cudaStream_t);
@@ -686,9 +695,8 @@ cudaError_t launch_bwd_prepass_strided(const __nv_bfloat16* o, const __nv_bfloat
     const int tpr = d / 8;
     if (d % 8 != 0 || tpr > 32 || (tpr & (tpr - 1)) != 0 || !lse || !lse2 || !zero) return cudaErrorInvalidValue;
     const long long threads = rows * tpr;
-    bwd_prepass_strided_kernel<<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(o, dO, lse, D, lse2, zero, rows, d, T,
-                                                                                         H, lt, lh, lb);
-    return cudaGetLastError();
+    return launch_pdl(bwd_prepass_strided_kernel, dim3((unsigned int)((threads + 255) / 256)), dim3(256), 0, stream, o, dO, lse, D,
+                      lse2, zero, rows, d, T, H, lt, lh, lb);
 }
 
 cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, long long rows, int d, int T, int H,
@@ -696,8 +704,8 @@ cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, lo
     if (rows == 0) return cudaSuccess;
     if (d % 8 != 0) return cudaErrorInvalidValue;
     const long long threads = rows * (d / 8);
-    dq_convert_strided_kernel<<<(unsigned int)((threads + 255) / 256), 256, 0, stream>>>(dq_acc, dq, rows, d, T, H, lt, lh, lb);
-    return cudaGetLastError();
+    return launch_pdl(dq_convert_strided_kernel, dim3((unsigned int)((threads + 255) / 256)), dim3(256), 0, stream, dq_acc, dq, rows,
+                      d, T, H, lt, lh, lb);
 }
 
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {

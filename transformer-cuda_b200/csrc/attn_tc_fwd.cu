@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    pdl_launch_dependents();
 
     const int n_q_tiles = (a.T + kBM - 1) / kBM;
     // CTA order: the last query tile of a slab is the longest. Longest-first across all slabs when the
@@ -128,6 +129,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_slot;
+    // barriers, TMEM and the tensor maps are set up: from here on global memory is touched, so wait for the
+    // kernel in front of this one in the stream (returns at once for an ordinary launch)
+    pdl_wait();
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
@@ -356,8 +360,7 @@ cudaError_t launch_fwd(const TcFwdArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const int n_q_tiles = (a.T + kBM - 1) / kBM;
     const long long blocks = (long long)n_q_tiles * a.BH;
-    kern<<<(unsigned int)blocks, kThreads, Cfg::kSmemBytes, stream>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, dim3((unsigned int)blocks), dim3(kThreads), Cfg::kSmemBytes, stream, a);
 }
 
 }  // namespace

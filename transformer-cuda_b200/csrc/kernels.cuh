@@ -9,6 +9,26 @@
 
 namespace b200attn {
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream is
+// still draining (its prologue then overlaps the predecessor's tail). Kernels launched this way execute
+// griddepcontrol.wait (pdl_wait() in tc_common.cuh) before their first global-memory access, so the data
+// dependency through the stream is unchanged. Used for the kernels of the BF16 forward/backward chain, where the
+// gaps between five short launches are a measurable share of a step.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------ layout_kernels.cu
 // TOut is float or __nv_bfloat16 for the split, TIn likewise for the merges.
 template <typename TOut>

@@ -171,6 +171,9 @@ __global__ void __launch_bounds__(kThreads) head_transpose_kernel(const THead* _
 __global__ void __launch_bounds__(kThreads) f32_to_bf16_kernel(const float* __restrict__ src,
                                                               __nv_bfloat16* __restrict__ dst, long long n8,
                                                               long long n) {
+    // the last kernel of the BF16 backward chain: launched with programmatic serialisation (see launch_pdl)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     long long g = blockIdx.x * (long long)kThreads + threadIdx.x;
     if (g < n8) {
         float a[8];
@@ -293,8 +296,7 @@ cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n
     bool vec_ok = aligned16(src) && aligned16(dst);
     long long n8 = vec_ok ? n / 8 : 0;
     long long work = n8 + (n - n8 * 8);
-    f32_to_bf16_kernel<<<blocks_for(work), kThreads, 0, stream>>>(src, dst, n8, n);
-    return cudaGetLastError();
+    return launch_pdl(f32_to_bf16_kernel, dim3(blocks_for(work)), dim3(kThreads), 0, stream, src, dst, n8, n);
 }
 
 cudaError_t launch_fill_normal_f32(float* dst, long long n, unsigned long long seed, long long offset,

@@ -26,6 +26,12 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch. launch_dependents: the next kernel in the stream may start being scheduled once
+// every CTA of this grid has passed this point (or exited). wait: blocks until the grids this one depends on have
+// completed and their memory is visible; returns at once when the kernel was launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // One lane of a converged warp. The MMA warps branch on this, not on `lane == 0`: measured on a B200,
 // the same tcgen05.mma sequence (the backward's 32 MMAs per step at d = 64) issues in 1557 cycles
 // behind elect.sync and in 2169 cycles behind a lane-id compare, i.e. the latter is issue-bound at

@@ -227,9 +227,10 @@ def fill_normal_(t, seed, offset=0):
     return t
 
 
-def kernel_timing(enable):
-    """Start (True) or stop (False) per-launch event timing of the tensor-core kernels; clears records."""
-    _lib.call("b200attn_kernel_timing", 1 if enable else 0)
+def kernel_timing(enable, every=1):
+    """Start (True) or stop (False) event timing of the tensor-core kernels, on every `every`-th launch of
+    each kernel; clears records."""
+    _lib.call("b200attn_kernel_timing", int(every) if enable else 0)
 
 
 def kernel_times():
