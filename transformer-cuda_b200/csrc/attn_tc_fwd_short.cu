@@ -1,5 +1,5 @@
-// SHORT-SEQUENCE variant of the causal attention forward (used for T <= 2048; attn_tc_fwd.cu has the
-// long-sequence variant and the description of the computation). Same math, same TMEM/TMA/MMA
+// TWO-CTAS-PER-SM variant of the causal attention forward (used for d = 64 at every T and for d = 128 up to
+// T = 4096; attn_tc_fwd.cu has the one-large-CTA variant for longer d = 128 sequences and the dispatch). Same math, same TMEM/TMA/MMA
 // idioms, different occupancy trade: a CTA here is small enough (256 TMEM columns, <= 96 KB of shared
 // memory, 192 threads) for TWO to be resident per SM, so that the prologue and epilogue of one CTA -
 // a large share of a CTA's life when it only walks a handful of key tiles - overlap the main loop of

@@ -87,7 +87,7 @@ struct TcFwdArgs {
     unsigned int* fault_word;
 };
 cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream);        // picks the variant by T
-cudaError_t launch_attn_fwd_tc_short(const TcFwdArgs& a, cudaStream_t stream);  // two CTAs per SM, T <= 2048
+cudaError_t launch_attn_fwd_tc_short(const TcFwdArgs& a, cudaStream_t stream);  // two CTAs per SM (d = 64; d = 128 up to T = 4096)
 
 struct TcBwdArgs {
     CUtensorMap map_q, map_k, map_v, map_do;  // BF16
