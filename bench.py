@@ -412,6 +412,32 @@ def main():
     ms_total = pdist.max_over_ranks(e0.elapsed_time(e1), device=dev)
     kt = ops.kernel_times()
     ops.kernel_timing(False)
+
+    # ---- the same step replayed from a CUDA graph (the reference's benchmark has such a mode,
+    # src/benchmark.cu:158-175): only reported for steps short enough for launch overhead to matter
+    graph_ms = None
+    if ms_total / args.steps < 1.0:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graphs = []
+            for s_ in sets:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step(s_)
+                graphs.append(g)
+            for i in range(max(3, args.warmup)):
+                graphs[i % n_sets].replay()
+            side.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(side)
+            for i in range(args.steps):
+                graphs[i % n_sets].replay()
+            g1.record(side)
+            side.synchronize()
+        torch.cuda.current_stream().wait_stream(side)
+        graph_ms = pdist.max_over_ranks(g0.elapsed_time(g1), device=dev) / args.steps
+        ops.check_device_fault()
     clocks = sampler.stop() if sampler else None
     ops.check_device_fault()
     ms_per_step = ms_total / args.steps
@@ -506,6 +532,9 @@ def main():
                                         "frac": fwd_tf / peaks["bf16"]}},
         "clocks": clocks,
     }
+    if graph_ms is not None:
+        line["cuda_graph_replay"] = {"ms_per_step": graph_ms, "value": all_flops / (graph_ms * 1e-3) / 1e12, "unit": UNIT,
+                                     "note": "the same K steps, each buffer set's forward+backward captured once and replayed"}
     if world == 1 and not args.no_cpu_baseline:  # the CPU arm runs beside the 1-GPU measurement only
         line["cpu_baseline"] = cpu_baseline(B, H, T, d, args.cpu_budget_s)
     print(json.dumps(line), flush=True)
