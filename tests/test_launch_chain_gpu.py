@@ -120,3 +120,29 @@ def test_packed_chain_back_to_back(pkg):
         for key in ("o", "dk", "dv"):
             assert torch.equal(slab[key], want_slab[key])
     ops.check_device_fault()
+
+
+@pytest.mark.parametrize("BH,T,d,iters", [(96, 1024, 64, 80), (8, 2048, 128, 20)])
+def test_fresh_inputs_every_step(pkg, BH, T, d, iters):
+    """New values in newly allocated memory before every step, kernels right behind the fills, no
+    synchronisation; then the same step again with the stream drained around each call. A kernel that
+    read a tile before its producer had finished - another kernel, or an earlier step of the same CTA
+    (the dS^T tile in shared memory, for one, is rewritten every step while dK / dQ of the step before
+    may still be reading it) - shows up as a difference."""
+    ops = pkg.ops
+    scale = 1.0 / math.sqrt(d)
+    for it in range(iters):
+        q, k, v, dO = (ops.fill_normal_(torch.empty(BH, T, d, device="cuda", dtype=BF16), seed=1000 * it + i)
+                       for i in range(4))
+        o, lse = ops.attention_forward_bf16(q, k, v, scale)
+        dq, dk, dv = ops.attention_backward_bf16(q, k, v, o, dO, lse, scale)
+        got = [t.clone() for t in (o, lse, dk, dv, dq)]
+        torch.cuda.synchronize()
+        o2, lse2 = ops.attention_forward_bf16(q, k, v, scale)
+        torch.cuda.synchronize()
+        dq2, dk2, dv2 = ops.attention_backward_bf16(q, k, v, o2, dO, lse2, scale)
+        torch.cuda.synchronize()
+        for name, g, r in zip(("o", "lse", "dk", "dv"), got, (o2, lse2, dk2, dv2)):
+            assert torch.equal(g, r), (it, name)
+        assert (got[4].float() - dq2.float()).abs().max().item() <= 2.0 ** -6 * max(1.0, dq2.float().abs().max().item()), it
+    ops.check_device_fault()

@@ -429,6 +429,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
 
             // ---- dS^T
             mbar_wait(&bars.dp_full, it & 1, &abort_flag, a.fault_word, 0x62);
+            // the dS^T tile in shared memory is still being read by dK / dQ of the previous step until the
+            // commit behind that dQ has arrived (at d = 128 the drain above has already waited for it)
+            if (!Cfg::kDqAliased && it > 0) mbar_wait(&bars.dq_full, (it - 1) & 1, &abort_flag, a.fault_word, 0x66);
             tc_fence_after();
             if (tid == 0) BWD_TRACE(1, it, 5);
             if (tid == 255) BWD_TRACE(2, it, 5);
