@@ -174,7 +174,12 @@ def run_gpt_step(args):
     JSON line. `--impl reference` runs the same harness linked against the reference's own attention kernels."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    name = "gpt_step_dp_ref" if args.impl == "reference" else "gpt_step_dp_b200"
+    # --gemm reference: the reference's FP32 cuBLAS wrappers; fp32 / bf16: the GEMM drop-in
+    # (transformer-cuda_b200/gemm/matmul_dropin.cu) in that arithmetic
+    if args.impl == "reference":
+        name = "gpt_step_dp_ref"
+    else:
+        name = "gpt_step_dp_b200" if args.gemm == "reference" else "gpt_step_dp_b200_gemm"
     exe = os.path.join(ROOT, "oracle", "_ref", name)
     if not os.path.exists(exe):
         if rank == 0:
@@ -184,6 +189,8 @@ def run_gpt_step(args):
     steps = max(1, min(args.steps, 20))
     env = dict(os.environ)
     env.setdefault("B200ATTN_MATH", "bf16")  # attention through the tcgen05 kernels (the reference arm ignores it)
+    if args.gemm != "reference":
+        env["B200GEMM_MATH"] = args.gemm
     res = subprocess.run([exe, "--steps", str(steps), "--warmup", str(min(args.warmup, 3))], env=env, capture_output=True, text=True)
     if res.returncode != 0:
         raise SystemExit(f"{name} failed on rank {rank}: {res.stderr[-2000:]}")
@@ -192,10 +199,14 @@ def run_gpt_step(args):
     child = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
     line = {"metric": "gpt_step_tokens_per_s", "value": child["value"], "unit": "tokens/s", "n_gpus": world, "steps": steps,
             "warmup": min(args.warmup, 3), "ms_per_step": child["ms_per_step"], "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 model, bf16 attention" if args.impl != "reference" else "f32",
+            "vs_baseline": None,
+            "dtype": "f32" if args.impl == "reference" else
+                     ("f32 buffers, bf16 attention and bf16 GEMM operands" if args.gemm == "bf16" else "f32 model, bf16 attention"),
             "data": "synthetic", "impl": args.impl,
             "config": {"workload": "c4: GPT training step L=12 C=768 H=12 d_ff=3072 V=50257 T=1024, per-GPU B=16, AdamW, "
-                                   "data-parallel NCCL all-reduce of gradients", **child["config"], "attention": child["attention"]},
+                                   "data-parallel NCCL all-reduce of gradients", **child["config"], "attention": child["attention"],
+                       "gemm": "reference FP32 cuBLAS wrappers" if (args.impl == "reference" or args.gemm == "reference")
+                               else f"GEMM drop-in, B200GEMM_MATH={args.gemm}"},
             "loss_after_last_step": child["loss"]}
     print(json.dumps(line), flush=True)
 
@@ -331,6 +342,8 @@ def main():
                     help="c2 (default), c3, c5_*: the attention path; c4: the data-parallel GPT training step around it")
     ap.add_argument("--cpu-budget-s", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm", default="bf16", choices=["reference", "fp32", "bf16"],
+                    help="c4 only: the model's GEMM wrappers - the reference's own FP32 ones, or the drop-in in FP32 / BF16 arithmetic")
     ap.add_argument("--kernel-event-stride", type=int, default=32,
                     help="bracket every N-th launch of each tensor-core kernel with CUDA events inside the timed region "
                          "(roofline durations); events between kernels undo their back-to-back launch, so N=1 slows the step")

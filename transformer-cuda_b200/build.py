@@ -16,6 +16,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 SO = os.path.join(LIBDIR, "libb200attn.so")
 AR = os.path.join(LIBDIR, "libb200attn.a")
+GEMM_AR = os.path.join(LIBDIR, "libb200gemm.a")
 
 
 def _nvcc():
@@ -64,6 +65,16 @@ def build(verbose=False, force=False, ptxas_info=False):
         if os.path.exists(AR):
             os.remove(AR)
         subprocess.check_call(["ar", "rcs", AR] + objs)
+    # the GEMM drop-in for the reference model (links against cuBLAS, so it stays out of libb200attn)
+    gemm_src = os.path.join(HERE, "gemm", "matmul_dropin.cu")
+    gemm_obj = os.path.join(OBJDIR, "matmul_dropin.o")
+    gemm_hdr = os.path.join(HERE, "..", "include", "kernels", "matmul.cuh")
+    if force or _stale(gemm_obj, [gemm_src, gemm_hdr]):
+        subprocess.check_call([nvcc] + ARCH + FLAGS + ["-I", os.path.join(HERE, "..", "include"), "-c", gemm_src, "-o", gemm_obj])
+    if force or _stale(GEMM_AR, [gemm_obj]):
+        if os.path.exists(GEMM_AR):
+            os.remove(GEMM_AR)
+        subprocess.check_call(["ar", "rcs", GEMM_AR, gemm_obj])
     return SO
 
 

@@ -1,0 +1,213 @@
+// GEMM wrappers of the reference model (include/kernels/matmul.cuh of sarimahsan/transformer-cuda) with a
+// selectable arithmetic: FP32 SIMT as in the reference (src/kernels/matmul.cu:30,96,196) or BF16 tensor
+// cores with FP32 accumulation on the same FP32 buffers. These are plain library GEMMs (cuBLAS /
+// cuBLASLt); the point of this file is that the data-parallel training step around the attention engine
+// is no longer dominated by FP32 SGEMMs on the CUDA cores. Row-major matrices are handed to the
+// column-major libraries as their transposes: C^T (N x M) = op(B)^T op(A)^T.
+//
+// Built into its own static library (libb200gemm.a); libb200attn does not depend on cuBLAS.
+#include "kernels/matmul.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+enum class Math { kFp32, kBf16 };
+
+Math math_mode() {
+    static const Math mode = [] {
+        const char* e = getenv("B200GEMM_MATH");
+        return (e && (!strcmp(e, "bf16") || !strcmp(e, "BF16"))) ? Math::kBf16 : Math::kFp32;
+    }();
+    return mode;
+}
+cublasComputeType_t compute_type() {
+    return math_mode() == Math::kBf16 ? CUBLAS_COMPUTE_32F_FAST_16BF : CUBLAS_COMPUTE_32F;
+}
+
+void report(const char* what, int status) {
+    if (status != 0) fprintf(stderr, "b200gemm: %s failed with status %d\n", what, status);
+}
+
+void bind_stream(cublasHandle_t handle, cudaStream_t stream) {
+    cudaStream_t cur = nullptr;
+    cublasGetStream(handle, &cur);
+    if (cur != stream) report("cublasSetStream", (int)cublasSetStream(handle, stream));
+}
+
+// ---------------------------------------------------------------- cuBLASLt plans, one per problem shape
+struct PlanKey {
+    int M, N, K, transA, transB, epilogue;
+    bool operator==(const PlanKey& o) const {
+        return M == o.M && N == o.N && K == o.K && transA == o.transA && transB == o.transB && epilogue == o.epilogue;
+    }
+};
+struct PlanKeyHash {
+    size_t operator()(const PlanKey& k) const {
+        size_t h = 1469598103934665603ull;
+        for (int v : {k.M, k.N, k.K, k.transA, k.transB, k.epilogue}) h = (h ^ size_t(unsigned(v))) * 1099511628211ull;
+        return h;
+    }
+};
+struct Plan {
+    cublasLtMatmulDesc_t op = nullptr;
+    cublasLtMatrixLayout_t a = nullptr, b = nullptr, c = nullptr;  // of the column-major problem: a <- B, b <- A
+    cublasLtMatmulAlgo_t algo;
+    bool has_algo = false;
+};
+std::unordered_map<PlanKey, Plan, PlanKeyHash> g_plans;
+std::mutex g_plans_mutex;
+
+bool build_plan(cublasLtHandle_t lt, const PlanKey& key, cublasComputeType_t ctype, size_t workspace_size, Plan* out) {
+    Plan p;
+    const cublasOperation_t opA = key.transA ? CUBLAS_OP_T : CUBLAS_OP_N;
+    const cublasOperation_t opB = key.transB ? CUBLAS_OP_T : CUBLAS_OP_N;
+    if (cublasLtMatmulDescCreate(&p.op, ctype, CUDA_R_32F) != CUBLAS_STATUS_SUCCESS) return false;
+    cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &opB, sizeof(opB));
+    cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &opA, sizeof(opA));
+    const cublasLtEpilogue_t epi = (cublasLtEpilogue_t)key.epilogue;
+    if (epi != CUBLASLT_EPILOGUE_DEFAULT) cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_EPILOGUE, &epi, sizeof(epi));
+    // row-major op(B) is K x N with leading dimension ldb; seen column-major it is the matrix below
+    const int lda = key.transA ? key.M : key.K, ldb = key.transB ? key.K : key.N, ldc = key.N;
+    cublasLtMatrixLayoutCreate(&p.a, CUDA_R_32F, key.transB ? key.K : key.N, key.transB ? key.N : key.K, ldb);
+    cublasLtMatrixLayoutCreate(&p.b, CUDA_R_32F, key.transA ? key.M : key.K, key.transA ? key.K : key.M, lda);
+    cublasLtMatrixLayoutCreate(&p.c, CUDA_R_32F, key.N, key.M, ldc);
+    cublasLtMatmulPreference_t pref = nullptr;
+    cublasLtMatmulPreferenceCreate(&pref);
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &workspace_size, sizeof(workspace_size));
+    cublasLtMatmulHeuristicResult_t res = {};
+    int found = 0;
+    const cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(lt, p.op, p.a, p.b, p.c, p.c, pref, 1, &res, &found);
+    cublasLtMatmulPreferenceDestroy(pref);
+    p.has_algo = (st == CUBLAS_STATUS_SUCCESS && found > 0);
+    if (p.has_algo) p.algo = res.algo;
+    *out = p;
+    return p.has_algo;
+}
+
+void destroy_plan(Plan& p) {
+    if (p.a) cublasLtMatrixLayoutDestroy(p.a);
+    if (p.b) cublasLtMatrixLayoutDestroy(p.b);
+    if (p.c) cublasLtMatrixLayoutDestroy(p.c);
+    if (p.op) cublasLtMatmulDescDestroy(p.op);
+    p = Plan();
+}
+
+// ---------------------------------------------------------------- bias kernels
+// Y[r][c] += bias[c], four columns per thread when N allows it.
+template <int VEC>
+__global__ void __launch_bounds__(256) add_bias_kernel(float* __restrict__ Y, const float* __restrict__ bias, long long groups,
+                                                       int n_groups_per_row) {
+    const long long g = blockIdx.x * 256ll + threadIdx.x;
+    if (g >= groups) return;
+    const int col = int(g % n_groups_per_row) * VEC;
+    if constexpr (VEC == 4) {
+        float4 y = reinterpret_cast<float4*>(Y)[g];
+        const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col));
+        y.x += b.x, y.y += b.y, y.z += b.z, y.w += b.w;
+        reinterpret_cast<float4*>(Y)[g] = y;
+    } else {
+        Y[g] += __ldg(bias + col);
+    }
+}
+
+// dbias[c] += sum_r dY[r][c]. A CTA owns 32 columns and a strip of rows; each warp walks its rows with
+// coalesced 128-byte reads, the eight warps meet in shared memory, one atomic per column and CTA.
+__global__ void __launch_bounds__(256) bias_backward_kernel(const float* __restrict__ dY, float* __restrict__ dbias, int M,
+                                                            int N, int rows_per_cta) {
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col = blockIdx.x * 32 + lane;
+    const int r0 = blockIdx.y * rows_per_cta;
+    const int r1 = min(M, r0 + rows_per_cta);
+    float s0 = 0.f, s1 = 0.f;
+    if (col < N) {
+        int r = r0 + warp;
+        for (; r + 8 < r1; r += 16) {
+            s0 += __ldg(dY + (long long)r * N + col);
+            s1 += __ldg(dY + (long long)(r + 8) * N + col);
+        }
+        if (r < r1) s0 += __ldg(dY + (long long)r * N + col);
+    }
+    part[warp][lane] = s0 + s1;
+    __syncthreads();
+    if (warp == 0 && col < N) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += part[w][lane];
+        atomicAdd(dbias + col, s);
+    }
+}
+
+}  // namespace
+
+void matmul_forward(cublasHandle_t handle, const float* A, const float* B, float* C, int M, int N, int K, bool transA,
+                    bool transB, float alpha, float beta, cudaStream_t stream) {
+    bind_stream(handle, stream);
+    const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
+    report("cublasGemmEx", (int)cublasGemmEx(handle, transB ? CUBLAS_OP_T : CUBLAS_OP_N, transA ? CUBLAS_OP_T : CUBLAS_OP_N, N, M,
+                                             K, &alpha, B, CUDA_R_32F, ldb, A, CUDA_R_32F, lda, &beta, C, CUDA_R_32F, ldc,
+                                             compute_type(), CUBLAS_GEMM_DEFAULT));
+}
+
+void matmul_batched_strided(cublasHandle_t handle, const float* A, const float* B, float* C, int M, int N, int K,
+                            long long int strideA, long long int strideB, long long int strideC, int batch_count, bool transA,
+                            bool transB, float alpha, float beta, cudaStream_t stream) {
+    bind_stream(handle, stream);
+    const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
+    report("cublasGemmStridedBatchedEx",
+           (int)cublasGemmStridedBatchedEx(handle, transB ? CUBLAS_OP_T : CUBLAS_OP_N, transA ? CUBLAS_OP_T : CUBLAS_OP_N, N, M, K,
+                                           &alpha, B, CUDA_R_32F, ldb, strideB, A, CUDA_R_32F, lda, strideA, &beta, C, CUDA_R_32F,
+                                           ldc, strideC, batch_count, compute_type(), CUBLAS_GEMM_DEFAULT));
+}
+
+void matmul_cublaslt(cublasLtHandle_t lt_handle, const float* A, const float* B, float* C, int M, int N, int K,
+                     cublasLtEpilogue_t epilogue, const float* bias, void* workspace, size_t workspace_size, bool transA,
+                     bool transB, float alpha, float beta, cudaStream_t stream) {
+    if (workspace == nullptr) workspace_size = 0;
+    const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, (int)epilogue};
+    Plan plan;
+    {
+        std::lock_guard<std::mutex> lock(g_plans_mutex);
+        auto it = g_plans.find(key);
+        if (it == g_plans.end()) {
+            Plan p;
+            if (!build_plan(lt_handle, key, compute_type(), workspace_size, &p) && math_mode() == Math::kBf16) {
+                destroy_plan(p);  // no tensor-core algorithm for this shape / epilogue: FP32 arithmetic for it
+                build_plan(lt_handle, key, CUBLAS_COMPUTE_32F, workspace_size, &p);
+            }
+            it = g_plans.emplace(key, p).first;
+        }
+        plan = it->second;
+        if (bias != nullptr) cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias));
+    }
+    report("cublasLtMatmul", (int)cublasLtMatmul(lt_handle, plan.op, &alpha, B, plan.a, A, plan.b, &beta, C, plan.c, C, plan.c,
+                                                 plan.has_algo ? &plan.algo : nullptr, workspace, workspace_size, stream));
+}
+
+void add_bias(float* Y, const float* bias, int M, int N, cudaStream_t stream) {
+    const long long total = (long long)M * N;
+    if (total == 0) return;
+    const bool vec = (N % 4 == 0) && ((reinterpret_cast<uintptr_t>(Y) | reinterpret_cast<uintptr_t>(bias)) & 15u) == 0;
+    if (vec) {
+        const long long groups = total / 4;
+        add_bias_kernel<4><<<(unsigned int)((groups + 255) / 256), 256, 0, stream>>>(Y, bias, groups, N / 4);
+    } else {
+        add_bias_kernel<1><<<(unsigned int)((total + 255) / 256), 256, 0, stream>>>(Y, bias, total, N);
+    }
+}
+
+void bias_backward(const float* dY, float* dbias, int M, int N, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return;
+    // enough row strips to fill the 148 SMs a few times over, at least 64 rows each
+    const int col_ctas = (N + 31) / 32;
+    int strips = (148 * 4 + col_ctas - 1) / col_ctas;
+    if (strips > (M + 63) / 64) strips = (M + 63) / 64;
+    if (strips < 1) strips = 1;
+    const int rows_per_cta = (M + strips - 1) / strips;
+    bias_backward_kernel<<<dim3(col_ctas, (M + rows_per_cta - 1) / rows_per_cta), 256, 0, stream>>>(dY, dbias, M, N, rows_per_cta);
+}
