@@ -1,0 +1,132 @@
+// Checker for the GEMM drop-in (transformer-cuda_b200/gemm/matmul_dropin.cu); test infrastructure, not product.
+// Runs every wrapper declared in include/kernels/matmul.cuh on seeded inputs and compares with a plain FP64
+// host computation of C = alpha * op(A) op(B) + beta * C on a sample of output elements. Shapes include
+// leading dimensions that are not multiples of four floats (the language-model head of the reference model,
+// V = 50257), large enough to take the staged BF16 path when B200GEMM_MATH=bf16.
+// Prints one JSON line per case: {"case": ..., "max_rel": ..., "ok": ...}; exit code 0 iff all are within tolerance.
+// usage: gemm_check [tolerance]   (default 1e-5 relative to the row/column scale; pass 2e-2 for BF16 arithmetic)
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "kernels/matmul.cuh"
+
+#define CK(x)                                                                              \
+    do {                                                                                   \
+        cudaError_t e_ = (x);                                                              \
+        if (e_ != cudaSuccess) {                                                           \
+            printf("CUDA error %s at line %d\n", cudaGetErrorString(e_), __LINE__);        \
+            exit(2);                                                                       \
+        }                                                                                  \
+    } while (0)
+
+static unsigned long long g_state = 88172645463325252ull;
+static float next_uniform() {  // xorshift64, values in [-1, 1)
+    g_state ^= g_state << 13;
+    g_state ^= g_state >> 7;
+    g_state ^= g_state << 17;
+    return float((g_state >> 11) & 0xFFFFFF) / float(0x800000) - 1.0f;
+}
+
+struct Case {
+    const char* name;
+    int M, N, K;
+    bool transA, transB;
+    float alpha, beta;
+    int api;  // 0 matmul_forward, 1 matmul_cublaslt, 2 matmul_cublaslt + BIAS epilogue
+};
+
+int main(int argc, char** argv) {
+    const double tol = argc > 1 ? atof(argv[1]) : 1e-5;
+    cublasHandle_t handle;
+    cublasLtHandle_t lt;
+    if (cublasCreate(&handle) != CUBLAS_STATUS_SUCCESS || cublasLtCreate(&lt) != CUBLAS_STATUS_SUCCESS) return 2;
+    void* workspace;
+    const size_t ws_bytes = 32u << 20;
+    CK(cudaMalloc(&workspace, ws_bytes));
+    const Case cases[] = {
+        {"aligned_small", 96, 128, 64, false, false, 1.0f, 0.0f, 0},
+        {"aligned_lt_bias", 256, 384, 128, false, false, 1.0f, 0.0f, 2},
+        {"transA_beta", 64, 96, 200, true, false, 0.5f, 1.0f, 1},
+        {"head_forward_unaligned", 2048, 50257, 768, false, false, 1.0f, 0.0f, 1},   // logits = X W
+        {"head_dw_unaligned", 768, 50257, 2048, true, false, 1.0f, 0.0f, 1},          // dW = X^T dlogits
+        {"head_dx_unaligned", 2048, 768, 50257, false, true, 1.0f, 0.0f, 0},          // dX = dlogits W^T
+        {"unaligned_small", 33, 77, 45, false, true, 1.0f, 0.0f, 0},
+    };
+    bool all_ok = true;
+    for (const Case& c : cases) {
+        const size_t na = size_t(c.M) * c.K, nb = size_t(c.K) * c.N, nc = size_t(c.M) * c.N;
+        std::vector<float> A(na), B(nb), C0(nc), bias(c.N), C(nc);
+        for (auto& x : A) x = next_uniform();
+        for (auto& x : B) x = next_uniform();
+        for (auto& x : C0) x = next_uniform();
+        for (auto& x : bias) x = next_uniform();
+        float *dA, *dB, *dC, *dbias;
+        CK(cudaMalloc(&dA, na * 4)); CK(cudaMalloc(&dB, nb * 4)); CK(cudaMalloc(&dC, nc * 4)); CK(cudaMalloc(&dbias, c.N * 4));
+        CK(cudaMemcpy(dA, A.data(), na * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(dB, B.data(), nb * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(dC, C0.data(), nc * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(dbias, bias.data(), c.N * 4, cudaMemcpyHostToDevice));
+        if (c.api == 0) matmul_forward(handle, dA, dB, dC, c.M, c.N, c.K, c.transA, c.transB, c.alpha, c.beta, 0);
+        else matmul_cublaslt(lt, dA, dB, dC, c.M, c.N, c.K, c.api == 2 ? CUBLASLT_EPILOGUE_BIAS : CUBLASLT_EPILOGUE_DEFAULT,
+                             c.api == 2 ? dbias : nullptr, workspace, ws_bytes, c.transA, c.transB, c.alpha, c.beta, 0);
+        CK(cudaDeviceSynchronize());
+        CK(cudaMemcpy(C.data(), dC, nc * 4, cudaMemcpyDeviceToHost));
+        // sample of outputs: corners, last column / row, and a seeded scatter
+        double max_rel = 0.0;
+        const int samples = 4000;
+        for (int s = 0; s < samples; ++s) {
+            int i, j;
+            if (s == 0) i = 0, j = 0;
+            else if (s == 1) i = c.M - 1, j = c.N - 1;
+            else if (s == 2) i = 0, j = c.N - 1;
+            else if (s == 3) i = c.M - 1, j = 0;
+            else i = int((next_uniform() * 0.5f + 0.5f) * c.M) % c.M, j = int((next_uniform() * 0.5f + 0.5f) * c.N) % c.N;
+            double acc = 0.0, scale = 0.0;
+            for (int k = 0; k < c.K; ++k) {
+                const double a = c.transA ? A[size_t(k) * c.M + i] : A[size_t(i) * c.K + k];
+                const double b = c.transB ? B[size_t(j) * c.K + k] : B[size_t(k) * c.N + j];
+                acc += a * b;
+                scale += fabs(a * b);
+            }
+            double want = c.alpha * acc + c.beta * C0[size_t(i) * c.N + j] + (c.api == 2 ? bias[j] : 0.0);
+            const double rel = fabs(double(C[size_t(i) * c.N + j]) - want) / (scale / sqrt(double(c.K)) + 1.0);
+            if (!(rel <= max_rel)) max_rel = rel;  // also catches NaN
+        }
+        const bool ok = max_rel <= tol;
+        all_ok = all_ok && ok;
+        printf("{\"case\": \"%s\", \"M\": %d, \"N\": %d, \"K\": %d, \"max_rel\": %.3e, \"ok\": %s}\n", c.name, c.M, c.N, c.K, max_rel,
+               ok ? "true" : "false");
+        cudaFree(dA); cudaFree(dB); cudaFree(dC); cudaFree(dbias);
+    }
+    // bias helpers
+    {
+        const int M = 1000, N = 50257;
+        std::vector<float> Y(size_t(M) * N), b(N), db(N, 0.25f);
+        for (auto& x : Y) x = next_uniform();
+        for (auto& x : b) x = next_uniform();
+        float *dY, *dbv, *ddb;
+        CK(cudaMalloc(&dY, Y.size() * 4)); CK(cudaMalloc(&dbv, N * 4)); CK(cudaMalloc(&ddb, N * 4));
+        CK(cudaMemcpy(dY, Y.data(), Y.size() * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(dbv, b.data(), N * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(ddb, db.data(), N * 4, cudaMemcpyHostToDevice));
+        bias_backward(dY, ddb, M, N, 0);  // accumulates onto 0.25
+        add_bias(dY, dbv, M, N, 0);
+        std::vector<float> Y2(Y.size()), db2(N);
+        CK(cudaDeviceSynchronize());
+        CK(cudaMemcpy(Y2.data(), dY, Y.size() * 4, cudaMemcpyDeviceToHost));
+        CK(cudaMemcpy(db2.data(), ddb, N * 4, cudaMemcpyDeviceToHost));
+        double e1 = 0, e2 = 0;
+        for (int j = 0; j < N; j += 97) {
+            double s = 0.25;
+            for (int i = 0; i < M; ++i) s += Y[size_t(i) * N + j];
+            e1 = fmax(e1, fabs(s - db2[j]));
+        }
+        for (size_t idx = 0; idx < Y.size(); idx += 1013) e2 = fmax(e2, fabs(double(Y[idx]) + b[idx % N] - Y2[idx]));
+        const bool ok = e1 <= 1e-3 && e2 <= 1e-6;
+        all_ok = all_ok && ok;
+        printf("{\"case\": \"bias_helpers\", \"bias_backward_max_abs\": %.3e, \"add_bias_max_abs\": %.3e, \"ok\": %s}\n", e1, e2, ok ? "true" : "false");
+    }
+    return all_ok ? 0 : 1;
+}

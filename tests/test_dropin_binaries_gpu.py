@@ -108,3 +108,16 @@ def test_gemm_dropin_on_the_tensor_cores(tmp_path):
     assert _max_abs(load("cuda_logits.bin"), load("pytorch_logits.bin")) <= 2e-2
     assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 5e-3
     assert _max_abs(got, ref) <= 2e-2
+
+
+@pytest.mark.parametrize("mode,tol", [("fp32", "1e-4"), ("bf16", "2e-2")])
+def test_gemm_wrappers_against_host_fp64(mode, tol):
+    """oracle/_ref/gemm_check: every wrapper of include/kernels/matmul.cuh on seeded inputs against an FP64 host
+    computation, including the language-model-head shapes (V = 50257: leading dimensions that are not a
+    multiple of 16 bytes), which in BF16 arithmetic take the staged path (padded BF16 operands, padded FP32
+    result copied into place)."""
+    res = subprocess.run([_binary("gemm_check"), tol], capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, B200GEMM_MATH=mode))
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "b200gemm:" not in res.stderr
+    assert res.stdout.count('"ok": true') == 8, res.stdout

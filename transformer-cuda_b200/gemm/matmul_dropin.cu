@@ -8,6 +8,8 @@
 // Built into its own static library (libb200gemm.a); libb200attn does not depend on cuBLAS.
 #include "kernels/matmul.cuh"
 
+#include <cuda_bf16.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -143,10 +145,142 @@ __global__ void __launch_bounds__(256) bias_backward_kernel(const float* __restr
     }
 }
 
+
+// ---------------------------------------------------------------- staged BF16 path for unaligned leading dimensions
+// The language-model head works on V = 50257 columns: rows of head_w, logits and d_logits start on 4-byte
+// boundaries only, which confines cuBLASLt to slow align-1 kernels (measured: 9.5 ms for each of the three
+// 1.26 TFLOP head GEMMs, 43 % of the BF16 step). In BF16 arithmetic such a GEMM is staged instead: operands are
+// converted once into BF16 scratch with leading dimensions padded to 16 bytes (padding zeroed), the product
+// goes to an FP32 tile with a padded leading dimension when C itself is unaligned, and one pass copies it
+// into place. Scratch is owned here, grown on demand and never shrunk.
+struct Scratch {
+    void* p = nullptr;
+    size_t bytes = 0;
+    void* get(size_t want) {
+        if (want > bytes) {
+            if (p) cudaFree(p);
+            p = nullptr, bytes = 0;
+            if (cudaMalloc(&p, want) != cudaSuccess) {
+                cudaGetLastError();
+                return nullptr;
+            }
+            bytes = want;
+        }
+        return p;
+    }
+};
+Scratch g_scratch;
+cublasLtHandle_t g_own_lt = nullptr;
+std::unordered_map<PlanKey, Plan, PlanKeyHash> g_staged_plans;
+constexpr size_t kStagedWorkspace = size_t(64) << 20;
+
+inline int round_up_int(int x, int m) { return (x + m - 1) / m * m; }
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+// FP32 (rows x cols, leading dimension ld_src) -> BF16 (rows_dst x ld_dst), everything outside rows x cols zeroed. One BF16
+// pair per thread: a warp reads 256 contiguous bytes and writes 128, whatever the alignment of the source rows.
+__global__ void __launch_bounds__(256) stage_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows,
+                                                         int cols, long long ld_src, int rows_dst, int ld_dst) {
+    const int pairs_per_row = ld_dst / 2;
+    const long long g = blockIdx.x * 256ll + threadIdx.x;
+    if (g >= (long long)rows_dst * pairs_per_row) return;
+    const int r = int(g / pairs_per_row), c0 = int(g % pairs_per_row) * 2;
+    const float* s = src + (long long)r * ld_src + c0;
+    const float a = (r < rows && c0 < cols) ? __ldg(s) : 0.f;
+    const float b = (r < rows && c0 + 1 < cols) ? __ldg(s + 1) : 0.f;
+    *reinterpret_cast<__nv_bfloat162*>(dst + (long long)r * ld_dst + c0) = __floats2bfloat162_rn(a, b);
+}
+
+// FP32 (rows x cols, padded leading dimension ld_src) -> FP32 (rows x cols, leading dimension ld_dst); one element per
+// thread, so loads and stores are both contiguous per warp.
+__global__ void __launch_bounds__(256) unpad_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols,
+                                                        int ld_src, long long ld_dst) {
+    const long long g = blockIdx.x * 256ll + threadIdx.x;
+    if (g >= (long long)rows * cols) return;
+    const int r = int(g / cols), c = int(g % cols);
+    dst[(long long)r * ld_dst + c] = __ldg(src + (long long)r * ld_src + c);
+}
+
+bool wants_staging(int M, int N, int K, bool transA, bool transB, float beta) {
+    if (math_mode() != Math::kBf16 || beta != 0.0f) return false;
+    const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
+    if (lda % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0) return false;
+    return (double)M * N * K >= double(1ull << 30);  // small products are not worth three extra passes
+}
+
+// Returns false when the staged path could not run (the caller then takes the direct path).
+bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, int K, bool transA, bool transB, float alpha,
+                      cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    if (!g_own_lt && cublasLtCreate(&g_own_lt) != CUBLAS_STATUS_SUCCESS) return false;
+    // The library only picks its fast kernels when the problem dimensions themselves are multiples of 8, so
+    // M, N and K are padded too (zero rows / columns; the extra part of the product is dropped by the copy back).
+    const int Mp = round_up_int(M, 8), Np = round_up_int(N, 8), Kp = round_up_int(K, 8);
+    // stored shapes (row-major): A is rowsA x colsA, B is rowsB x colsB
+    const int rowsA = transA ? K : M, colsA = transA ? M : K;
+    const int rowsB = transB ? N : K, colsB = transB ? K : N;
+    const int rowsA_p = transA ? Kp : Mp, lda_p = transA ? Mp : Kp;
+    const int rowsB_p = transB ? Np : Kp, ldb_p = transB ? Kp : Np;
+    const bool pad_c = (Np != N) || (Mp != M);
+    const int ldc_p = Np;
+    const size_t bytesA = align256(size_t(rowsA_p) * lda_p * 2), bytesB = align256(size_t(rowsB_p) * ldb_p * 2);
+    const size_t bytesC = pad_c ? align256(size_t(Mp) * ldc_p * 4) : 0;
+    uint8_t* base = static_cast<uint8_t*>(g_scratch.get(kStagedWorkspace + bytesA + bytesB + bytesC));
+    if (!base) return false;
+    void* workspace = base;
+    __nv_bfloat16* Ab = reinterpret_cast<__nv_bfloat16*>(base + kStagedWorkspace);
+    __nv_bfloat16* Bb = reinterpret_cast<__nv_bfloat16*>(base + kStagedWorkspace + bytesA);
+    float* Cp = pad_c ? reinterpret_cast<float*>(base + kStagedWorkspace + bytesA + bytesB) : C;
+
+    const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, -1};
+    auto it = g_staged_plans.find(key);
+    if (it == g_staged_plans.end()) {
+        Plan p;
+        const cublasOperation_t opA = transA ? CUBLAS_OP_T : CUBLAS_OP_N, opB = transB ? CUBLAS_OP_T : CUBLAS_OP_N;
+        bool ok = cublasLtMatmulDescCreate(&p.op, CUBLAS_COMPUTE_32F, CUDA_R_32F) == CUBLAS_STATUS_SUCCESS;
+        if (ok) {
+            cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &opB, sizeof(opB));
+            cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &opA, sizeof(opA));
+            cublasLtMatrixLayoutCreate(&p.a, CUDA_R_16BF, ldb_p, rowsB_p, ldb_p);  // row-major B seen column-major
+            cublasLtMatrixLayoutCreate(&p.b, CUDA_R_16BF, lda_p, rowsA_p, lda_p);
+            cublasLtMatrixLayoutCreate(&p.c, CUDA_R_32F, Np, Mp, ldc_p);
+            cublasLtMatmulPreference_t pref = nullptr;
+            cublasLtMatmulPreferenceCreate(&pref);
+            cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &kStagedWorkspace, sizeof(kStagedWorkspace));
+            cublasLtMatmulHeuristicResult_t res = {};
+            int found = 0;
+            ok = cublasLtMatmulAlgoGetHeuristic(g_own_lt, p.op, p.a, p.b, p.c, p.c, pref, 1, &res, &found) == CUBLAS_STATUS_SUCCESS && found > 0;
+            cublasLtMatmulPreferenceDestroy(pref);
+            if (ok) p.algo = res.algo, p.has_algo = true;
+        }
+        if (!ok) destroy_plan(p);
+        it = g_staged_plans.emplace(key, p).first;
+    }
+    const Plan& plan = it->second;
+    if (!plan.has_algo) return false;
+
+    const long long ga = (long long)rowsA_p * (lda_p / 2), gb = (long long)rowsB_p * (ldb_p / 2);
+    stage_bf16_kernel<<<(unsigned int)((ga + 255) / 256), 256, 0, stream>>>(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p);
+    stage_bf16_kernel<<<(unsigned int)((gb + 255) / 256), 256, 0, stream>>>(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p);
+    const float beta = 0.0f;
+    const cublasStatus_t st = cublasLtMatmul(g_own_lt, plan.op, &alpha, Bb, plan.a, Ab, plan.b, &beta, Cp, plan.c, Cp, plan.c,
+                                             &plan.algo, workspace, kStagedWorkspace, stream);
+    if (st != CUBLAS_STATUS_SUCCESS) {
+        report("cublasLtMatmul (staged BF16)", (int)st);
+        return false;
+    }
+    if (pad_c) {
+        const long long gc = (long long)M * N;
+        unpad_f32_kernel<<<(unsigned int)((gc + 255) / 256), 256, 0, stream>>>(Cp, C, M, N, ldc_p, N);
+    }
+    return true;
+}
+
 }  // namespace
 
 void matmul_forward(cublasHandle_t handle, const float* A, const float* B, float* C, int M, int N, int K, bool transA,
                     bool transB, float alpha, float beta, cudaStream_t stream) {
+    if (wants_staging(M, N, K, transA, transB, beta) && staged_bf16_gemm(A, B, C, M, N, K, transA, transB, alpha, stream)) return;
     bind_stream(handle, stream);
     const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
     report("cublasGemmEx", (int)cublasGemmEx(handle, transB ? CUBLAS_OP_T : CUBLAS_OP_N, transA ? CUBLAS_OP_T : CUBLAS_OP_N, N, M,
@@ -169,6 +303,9 @@ void matmul_cublaslt(cublasLtHandle_t lt_handle, const float* A, const float* B,
                      cublasLtEpilogue_t epilogue, const float* bias, void* workspace, size_t workspace_size, bool transA,
                      bool transB, float alpha, float beta, cudaStream_t stream) {
     if (workspace == nullptr) workspace_size = 0;
+    if (epilogue == CUBLASLT_EPILOGUE_DEFAULT && bias == nullptr && wants_staging(M, N, K, transA, transB, beta) &&
+        staged_bf16_gemm(A, B, C, M, N, K, transA, transB, alpha, stream))
+        return;
     const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, (int)epilogue};
     Plan plan;
     {
