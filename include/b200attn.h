@@ -48,7 +48,8 @@ int b200attn_reserve(int BH, int T, int d);
 /* Free the scratch of the current device (after synchronising it). */
 int b200attn_release(void);
 /* Synchronise the current device and report the fault word written by kernels whose bounded
- * waits ran out (0 = none); clears the word. `code` is a HOST pointer and may be NULL. */
+ * waits ran out (0 = none); clears the word. `code` is a HOST pointer and may be NULL. Allocates
+ * nothing (a device on which no entry point has run yet simply reports 0). */
 int b200attn_check_device_fault(unsigned int* code);
 
 /* Per-launch timing of the two tensor-core kernels, for roofline reporting: with enable = N > 0,
@@ -136,10 +137,15 @@ int b200attn_bwd_bf16_packed(const void* qkv, const void* out, const void* dout,
  * B200ATTN_NOALLOC_SCRATCH_BYTES that every GPU loading the library holds until exit; the call makes
  * no cudaMalloc/cudaFree or other allocating call. Limits: 256 + 4*BH*T*d + 8*BH*T bytes (each part
  * rounded up to 256) must fit in the array, else B200ATTN_ERR_UNSUPPORTED (the benchmark shape
- * BH=96, T=1024, d=64 fits); failures are also printed to stderr. All calls on a device share the
- * array, which keeps the previous call's contents (each call clears what must start from zero), so
- * calls that overlap on the GPU race. The first call on a device looks up the array's address and
- * clears its fault word synchronously: make it before any stream capture. */
+ * BH=96, T=1024, d=64 fits); b200attn_last_error() carries the text like for every other entry
+ * point. All calls on a device share the array, which keeps the previous call's contents (each call
+ * clears what must start from zero), so calls that overlap on the GPU race. The array also holds the
+ * fault word of this entry point's kernels; b200attn_check_device_fault reads and clears it without
+ * allocating. The first call on a device looks up the array's address - which makes the driver load
+ * the module there: the 32 MiB are taken from the device at that moment and the driver may
+ * synchronise - and clears the fault word synchronously. So make that first call at start-up, before
+ * the host's own pool claims the rest of the GPU and outside any stream capture (a first call that
+ * arrives while its stream is capturing returns B200ATTN_ERR_SCRATCH). */
 #define B200ATTN_NOALLOC_SCRATCH_BYTES (32u * 1024u * 1024u)
 int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dO,
                               const float* lse, void* dq, void* dk, void* dv, int BH, int T, int d, float scale,

@@ -92,14 +92,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
-bool stream_is_capturing(cudaStream_t s) {
-    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    return st != cudaStreamCaptureStatusNone;
-}
+using b200attn::stream_is_capturing;
 
 // Looks up (and on first use initialises) the state of the current device.
 int device_state(cudaStream_t stream, DeviceState** out) {
@@ -273,6 +266,18 @@ int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, con
 
 }  // namespace
 
+namespace b200attn {
+void set_last_error(const char* text) { snprintf(g_error, sizeof(g_error), "%s", text ? text : ""); }
+bool stream_is_capturing(cudaStream_t s) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &st) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return st != cudaStreamCaptureStatusNone;
+}
+}  // namespace b200attn
+
 // ====================================================================== library state
 extern "C" int b200attn_version(void) { return 100; }
 
@@ -308,17 +313,27 @@ extern "C" int b200attn_release(void) {
 }
 
 extern "C" int b200attn_check_device_fault(unsigned int* code) {
-    DeviceState* st = nullptr;
-    int rc = device_state(nullptr, &st);
-    if (rc) return rc;
+    // Two words can hold a fault: the heap word of the allocating entry points (it exists only once one of
+    // them has run on this device: this call must not be the one that allocates it, since hosts that use
+    // only b200attn_bwd_bf16_noalloc cannot allocate) and the word inside the static scratch array.
+    int dev = 0;
+    RETURN_IF_CUDA(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(B200ATTN_ERR_CUDA, "device index %d out of range", dev);
     RETURN_IF_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
-    unsigned int w = 0;
-    RETURN_IF_CUDA(cudaMemcpy(&w, st->fault_word, sizeof(w), cudaMemcpyDeviceToHost), "cudaMemcpy(fault word)");
-    if (code) *code = w;
-    if (w != 0) {
-        RETURN_IF_CUDA(cudaMemset(st->fault_word, 0, sizeof(w)), "cudaMemset(fault word)");
-        return fail(B200ATTN_ERR_DEVICE_FAULT, "a bounded wait inside a kernel ran out (fault word 0x%08x)", w);
+    unsigned int w = 0, w_static = 0;
+    unsigned int* heap_word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (g_dev[dev].ready) heap_word = g_dev[dev].fault_word;
     }
+    if (heap_word) {
+        RETURN_IF_CUDA(cudaMemcpy(&w, heap_word, sizeof(w), cudaMemcpyDeviceToHost), "cudaMemcpy(fault word)");
+        if (w != 0) RETURN_IF_CUDA(cudaMemset(heap_word, 0, sizeof(w)), "cudaMemset(fault word)");
+    }
+    RETURN_IF_CUDA(static_scratch_take_fault(&w_static), "reading the static scratch fault word");
+    if (w == 0) w = w_static;
+    if (code) *code = w;
+    if (w != 0) return fail(B200ATTN_ERR_DEVICE_FAULT, "a bounded wait inside a kernel ran out (fault word 0x%08x)", w);
     return B200ATTN_OK;
 }
 

@@ -124,4 +124,14 @@ cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, lo
 // dq (BF16) = dq_acc (FP32), elementwise.
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 
+// ------------------------------------------------------------------ host-side hooks between api.cu and static_scratch.cu
+// Stores `text` as the calling thread's last error, i.e. what b200attn_last_error() returns (api.cu).
+void set_last_error(const char* text);
+// True while `stream` is being captured into a graph (api.cu).
+bool stream_is_capturing(cudaStream_t stream);
+// Fault word of the static-scratch backward on the current device (static_scratch.cu). Copies the word to
+// *word and clears it on the device when it was set; *word = 0 when that entry point has not been used on
+// this device yet. The caller has synchronised the device. Allocates nothing.
+cudaError_t static_scratch_take_fault(unsigned int* word);
+
 }  // namespace b200attn

@@ -49,23 +49,26 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode_fn = nullptr;
 
-thread_local char g_noalloc_error[512] = "";
-
+// Formats the message and hands it to the buffer b200attn_last_error() returns for this thread.
 int fail(int code, const char* fmt, ...) {
+    char text[480];
     va_list ap;
     va_start(ap, fmt);
-    vsnprintf(g_noalloc_error, sizeof(g_noalloc_error), fmt, ap);
+    vsnprintf(text, sizeof(text), fmt, ap);
     va_end(ap);
-    // Leave the text where b200attn_last_error() finds it: report through a failing call of the
-    // public API would change that code path, so the message is also printed here.
-    fprintf(stderr, "[b200attn] b200attn_bwd_bf16_noalloc: %s\n", g_noalloc_error);
+    char full[512];
+    snprintf(full, sizeof(full), "b200attn_bwd_bf16_noalloc: %s", text);
+    set_last_error(full);
     return code;
 }
 
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// Set-up, once per device, with that device current.
-int setup_current_device(PerDevice** out) {
+// Set-up, once per device, with that device current. The first cudaGetSymbolAddress on a device makes the
+// driver load this module there, which is when the array's 32 MiB are taken from the device (and the
+// driver may synchronise); the memset below is synchronous too. Both are illegal inside a stream capture,
+// so a first call that arrives while `stream` is capturing is refused.
+int setup_current_device(cudaStream_t stream, PerDevice** out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
@@ -73,6 +76,8 @@ int setup_current_device(PerDevice** out) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     PerDevice& pd = g_per_device[dev];
     if (pd.base == nullptr) {
+        if (stream_is_capturing(stream))
+            return fail(B200ATTN_ERR_SCRATCH, "first call on device %d arrives inside a stream capture; make one call before capturing", dev);
         unsigned char* ptr = nullptr;
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
         if (e != cudaSuccess || ptr == nullptr)
@@ -116,6 +121,26 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
+namespace b200attn {
+cudaError_t static_scratch_take_fault(unsigned int* word) {
+    *word = 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        base = g_per_device[dev].base;
+    }
+    if (!base) return cudaSuccess;  // never used on this device: nothing to read, and nothing gets loaded
+    e = cudaMemcpy(word, base, sizeof(*word), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    if (*word != 0) e = cudaMemset(base, 0, sizeof(*word));
+    return e;
+}
+}  // namespace b200attn
+
 extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dO,
                                          const float* lse, void* dq, void* dk, void* dv, int BH, int T, int d,
                                          float scale, b200attn_stream_t stream_) {
@@ -128,14 +153,18 @@ extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const voi
         !aligned16(dk) || !aligned16(dv))
         return fail(B200ATTN_ERR_INVALID_ARGUMENT, "tensors must be 16-byte aligned");
     if (d != 64 && d != 128) return fail(B200ATTN_ERR_UNSUPPORTED, "d must be 64 or 128, got %d", d);
-    const size_t n = rows * size_t(d);
-    const size_t need = kFaultRegion + round_up(n * sizeof(float), 256) + 2 * round_up(rows * sizeof(float), 256);
-    if (need > kScratchBytes)
+    // size check in a form that cannot wrap: a row costs 4*d + 8 bytes, so first bound the row count by
+    // division, then (the products now being small) compute the exact demand with its 256-byte roundings
+    const size_t row_bytes = size_t(d) * sizeof(float) + 2 * sizeof(float);
+    const bool rows_fit = rows <= (kScratchBytes - kFaultRegion) / row_bytes;
+    const size_t n = rows_fit ? rows * size_t(d) : 0;
+    const size_t need = rows_fit ? kFaultRegion + round_up(n * sizeof(float), 256) + 2 * round_up(rows * sizeof(float), 256) : 0;
+    if (!rows_fit || need > kScratchBytes)
         return fail(B200ATTN_ERR_UNSUPPORTED,
-                    "shape BH=%d T=%d d=%d needs %zu bytes of scratch but the static array holds %zu; use b200attn_bwd_bf16 "
-                    "or split the (batch, head) slabs over several calls", BH, T, d, need, kScratchBytes);
+                    "shape BH=%d T=%d d=%d needs %zu rows of %zu bytes of scratch but the static array holds %zu bytes; use "
+                    "b200attn_bwd_bf16 or split the (batch, head) slabs over several calls", BH, T, d, rows, row_bytes, kScratchBytes);
     PerDevice* pd = nullptr;
-    int rc = setup_current_device(&pd);
+    int rc = setup_current_device(stream, &pd);
     if (rc) return rc;
     if (!pd->is_sm100) return fail(B200ATTN_ERR_UNSUPPORTED, "needs an sm_100a device (B200)");
 

@@ -115,14 +115,40 @@ def head_merge_transpose_backward(dout, din, B, H, T, d_head):
 
 
 # ------------------------------------------------------------------ BF16 tensor-core entry points
-def attention_forward_bf16(q, k, v, scale, out=None, lse=None):
-    """q,k,v: BF16 (..., T, d) with any leading (batch, head) dims; returns (out BF16, lse FP32 (..., T))."""
+def _slab_dims(q, others, stats):
+    """(BH, T, d) of q (..., T, d); every tensor of `others` must hold BH*T*d elements and every one of
+    `stats` BH*T, so that no tile store or reduction of the kernels can run past a caller's buffer."""
+    if q.dim() < 2:
+        raise _lib.B200AttnError(_lib.ERR_INVALID_ARGUMENT, "q: expected (..., T, d)")
     T, d = q.shape[-2], q.shape[-1]
     BH = q.numel() // (T * d) if T * d else 0
+    for t, nm in others:
+        if t.numel() != q.numel():
+            raise _lib.B200AttnError(_lib.ERR_INVALID_ARGUMENT, f"{nm}: has {t.numel()} elements, q has {q.numel()}")
+    for t, nm in stats:
+        _need(t, BH * T, nm)
+    return BH, T, d
+
+
+def _packed_dims(qkv, H):
+    """(B, T, d) of qkv (B, T, 3*H*d); a width that 3*H does not divide is an error, not a truncation."""
+    if qkv.dim() != 3 or H <= 0 or qkv.shape[2] % (3 * H) != 0:
+        raise _lib.B200AttnError(_lib.ERR_INVALID_ARGUMENT, f"qkv: expected (B, T, 3*H*d) with H={H}, got {tuple(qkv.shape)}")
+    return qkv.shape[0], qkv.shape[1], qkv.shape[2] // (3 * H)
+
+
+def _exact(t, numel, name):
+    if t.numel() != numel:
+        raise _lib.B200AttnError(_lib.ERR_INVALID_ARGUMENT, f"{name}: has {t.numel()} elements, needs {numel}")
+
+
+def attention_forward_bf16(q, k, v, scale, out=None, lse=None):
+    """q,k,v: BF16 (..., T, d) with any leading (batch, head) dims; returns (out BF16, lse FP32 (..., T))."""
     if out is None:
         out = torch.empty_like(q)
     if lse is None:
         lse = torch.empty(q.shape[:-1], dtype=F32, device=q.device)
+    BH, T, d = _slab_dims(q, ((k, "k"), (v, "v"), (out, "out")), ((lse, "lse"),))
     _lib.call("b200attn_fwd_bf16", _ptr(q, BF16, "q"), _ptr(k, BF16, "k"), _ptr(v, BF16, "v"), _ptr(out, BF16, "out"),
               _ptr(lse, F32, "lse"), BH, T, d, float(scale), _stream())
     return out, lse
@@ -130,11 +156,10 @@ def attention_forward_bf16(q, k, v, scale, out=None, lse=None):
 
 def attention_backward_bf16(q, k, v, o, dO, lse, scale, dq=None, dk=None, dv=None):
     """BF16 backward; returns (dq, dk, dv) BF16, overwritten."""
-    T, d = q.shape[-2], q.shape[-1]
-    BH = q.numel() // (T * d) if T * d else 0
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
+    BH, T, d = _slab_dims(q, ((k, "k"), (v, "v"), (o, "o"), (dO, "dO"), (dq, "dq"), (dk, "dk"), (dv, "dv")), ((lse, "lse"),))
     _lib.call("b200attn_bwd_bf16", _ptr(q, BF16, "q"), _ptr(k, BF16, "k"), _ptr(v, BF16, "v"), _ptr(o, BF16, "o"),
               _ptr(dO, BF16, "dO"), _ptr(lse, F32, "lse"), _ptr(dq, BF16, "dq"), _ptr(dk, BF16, "dk"),
               _ptr(dv, BF16, "dv"), BH, T, d, float(scale), _stream())
@@ -145,8 +170,7 @@ def attention_backward_bf16_noalloc(q, k, v, o, dO, lse, scale, dq, dk, dv):
     """The BF16 backward through the entry point that takes its scratch from the library's static
     device array instead of allocating (see include/b200attn.h for who needs it and its size limit).
     Output tensors are passed in, so this wrapper allocates nothing either."""
-    T, d = q.shape[-2], q.shape[-1]
-    BH = q.numel() // (T * d) if T * d else 0
+    BH, T, d = _slab_dims(q, ((k, "k"), (v, "v"), (o, "o"), (dO, "dO"), (dq, "dq"), (dk, "dk"), (dv, "dv")), ((lse, "lse"),))
     _lib.call("b200attn_bwd_bf16_noalloc", _ptr(q, BF16, "q"), _ptr(k, BF16, "k"), _ptr(v, BF16, "v"),
               _ptr(o, BF16, "o"), _ptr(dO, BF16, "dO"), _ptr(lse, F32, "lse"), _ptr(dq, BF16, "dq"),
               _ptr(dk, BF16, "dk"), _ptr(dv, BF16, "dv"), BH, T, d, float(scale), _stream())
@@ -156,10 +180,10 @@ def attention_backward_bf16_noalloc(q, k, v, o, dO, lse, scale, dq, dk, dv):
 def attention_forward_bf16_packed(qkv, H, scale, out=None, lse=None):
     """Attention straight on the projection output: qkv BF16 (B, T, 3*H*d) with inner order
     [Q heads | K heads | V heads]; returns (out BF16 (B, T, H*d), lse FP32 (B, H, T)). No split or merge pass."""
-    B, T, C3 = qkv.shape
-    d = C3 // (3 * H)
+    B, T, d = _packed_dims(qkv, H)
     out = torch.empty(B, T, H * d, device=qkv.device, dtype=BF16) if out is None else out
     lse = torch.empty(B, H, T, device=qkv.device, dtype=F32) if lse is None else lse
+    _exact(out, B * T * H * d, "out"); _need(lse, B * H * T, "lse")
     _lib.call("b200attn_fwd_bf16_packed", _ptr(qkv, BF16, "qkv"), _ptr(out, BF16, "out"), _ptr(lse, F32, "lse"),
               B, T, H, d, float(scale), _stream())
     return out, lse
@@ -167,9 +191,10 @@ def attention_forward_bf16_packed(qkv, H, scale, out=None, lse=None):
 
 def attention_backward_bf16_packed(qkv, out, dout, lse, H, scale, dqkv=None):
     """Backward of attention_forward_bf16_packed: dout BF16 (B, T, H*d) -> dqkv BF16 (B, T, 3*H*d), overwritten."""
-    B, T, C3 = qkv.shape
-    d = C3 // (3 * H)
+    B, T, d = _packed_dims(qkv, H)
     dqkv = torch.empty_like(qkv) if dqkv is None else dqkv
+    _exact(out, B * T * H * d, "out"); _exact(dout, B * T * H * d, "dout"); _exact(dqkv, qkv.numel(), "dqkv")
+    _need(lse, B * H * T, "lse")
     _lib.call("b200attn_bwd_bf16_packed", _ptr(qkv, BF16, "qkv"), _ptr(out, BF16, "out"), _ptr(dout, BF16, "dout"),
               _ptr(lse, F32, "lse"), _ptr(dqkv, BF16, "dqkv"), B, T, H, d, float(scale), _stream())
     return dqkv
@@ -210,6 +235,11 @@ def get_math_mode():
 
 def reserve(BH, T, d):
     _lib.call("b200attn_reserve", int(BH), int(T), int(d))
+
+
+def release():
+    """Free the library-owned scratch of the current device (synchronises it)."""
+    _lib.call("b200attn_release")
 
 
 def check_device_fault():
