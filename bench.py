@@ -328,6 +328,121 @@ def run_path_kernels(args, B, H, T, d):
     }), flush=True)
 
 
+class DeviceWorkload:
+    """Seeded BF16 Q, K, V, dO of one workload resident on one GPU (this rank's (batch, head) slabs of a batch
+    `world` times the per-GPU batch), rotating over enough buffer sets to exceed L2, and the forward + backward step."""
+
+    def __init__(self, pkg, dev, rank, world, B, H, T, d):
+        import torch
+        self.pkg, self.ops, self.dev, self.torch = pkg, pkg.ops, dev, torch
+        ops = self.ops
+        mine = pkg.shard.slab_range(B * H * world, rank, world)
+        self.BH, self.T, self.d = mine.count, T, d
+        self.n = self.BH * T * d
+        self.scale = 1.0 / math.sqrt(d)
+        bf16 = torch.bfloat16
+        self.set_bytes = 9 * self.n * 2  # q,k,v,o,dO,dq,dk,dv in BF16 + about one tensor of scratch traffic
+        self.n_sets = max(2, math.ceil(2.0 * L2_BYTES / self.set_bytes))  # a step's inputs were evicted from L2
+        self.sets = []
+        for s in range(self.n_sets):
+            ts = []
+            for i in range(4):  # q, k, v, dO: counter-based streams indexed by global element, distinct per set
+                t = torch.empty(self.BH, T, d, device=dev, dtype=bf16)
+                ops.fill_normal_(t, seed=1000 + 10 * s + i, offset=pkg.shard.element_offset(mine, T, d))
+                ts.append(t)
+            q, k, v, dO = ts
+            self.sets.append(dict(q=q, k=k, v=v, dO=dO, o=torch.empty_like(q), lse=torch.empty(self.BH, T, device=dev),
+                                  dq=torch.empty_like(q), dk=torch.empty_like(q), dv=torch.empty_like(q)))
+        ops.reserve(self.BH, T, d)
+
+    def step(self, s):
+        ops, scale = self.ops, self.scale
+        ops.attention_forward_bf16(s["q"], s["k"], s["v"], scale, s["o"], s["lse"])
+        ops.attention_backward_bf16(s["q"], s["k"], s["v"], s["o"], s["dO"], s["lse"], scale, s["dq"], s["dk"], s["dv"])
+
+    def timed_steps(self, steps, warmup, stride, sampler=None):
+        """`warmup` untimed steps, then exactly `steps` steps between barrier + synchronize on both sides, CUDA events on
+        the launching stream, maximum over ranks. Returns (total ms, per-kernel event times)."""
+        torch, ops = self.torch, self.ops
+        from transformer_cuda_b200 import dist as pdist
+        for i in range(warmup):
+            self.step(self.sets[i % self.n_sets])
+        torch.cuda.synchronize()
+        ops.check_device_fault()
+        if sampler:
+            sampler.wait_first_sample()
+        ops.kernel_timing(True, every=stride)
+        pdist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            self.step(self.sets[i % self.n_sets])
+        e1.record()
+        torch.cuda.synchronize()
+        pdist.barrier()
+        ms_total = pdist.max_over_ranks(e0.elapsed_time(e1), device=self.dev)
+        kt = ops.kernel_times()
+        ops.kernel_timing(False)
+        return ms_total, kt
+
+
+def fwd_kernel_name(T, d):
+    """The forward variant launch_attn_fwd_tc dispatches to (csrc/attn_tc_fwd.cu): the two-CTAs-per-SM kernel for
+    d = 64 and for d = 128 up to T = 4096, the one-CTA-per-SM kernel beyond."""
+    return "attn_fwd_tc_short_kernel" if (d == 64 or T <= 4096) else "attn_fwd_tc_kernel"
+
+
+def kernel_rooflines(kt, BH, T, d, peaks):
+    bwd_ms = kt["bwd_ms"] / max(1, kt["bwd_launches"])
+    fwd_ms = kt["fwd_ms"] / max(1, kt["fwd_launches"])
+    bwd_tf = 5.0 * BH * T * T * d / (bwd_ms * 1e-3) / 1e12 if bwd_ms > 0 else 0.0
+    fwd_tf = 2.0 * BH * T * T * d / (fwd_ms * 1e-3) / 1e12 if fwd_ms > 0 else 0.0
+    return bwd_ms, fwd_ms, bwd_tf, fwd_tf
+
+
+def extra_workloads(pkg, dev, rank, world, local, peaks, names):
+    """Device-timed forward + backward of the other benchmark shapes (long context, the scaling sweep), a short
+    run each (about half a second of steps after 3 warm-up steps), each with its own clock record."""
+    import torch
+    from transformer_cuda_b200 import dist as pdist
+    out = {}
+    for name in names:
+        B, H, T, d = WORKLOADS[name]
+        W = DeviceWorkload(pkg, dev, rank, world, B, H, T, d)
+        # calibrate the step count on three untimed steps
+        for i in range(3):
+            W.step(W.sets[i % W.n_sets])
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for i in range(3):
+            W.step(W.sets[i % W.n_sets])
+        c1.record()
+        torch.cuda.synchronize()
+        est = pdist.max_over_ranks(c0.elapsed_time(c1), device=dev) / 3
+        steps = int(max(8, min(400, math.ceil(500.0 / max(est, 1e-3)))))
+        sampler = ClockSampler(local) if rank == 0 else None
+        ms_total, kt = W.timed_steps(steps, 3, max(1, steps // 8), sampler)
+        clocks = sampler.stop() if sampler else None
+        ms = ms_total / steps
+        fl = pdist.sum_over_ranks(flops(1, W.BH, T, d), device=dev)
+        value = fl / (ms * 1e-3) / 1e12
+        bwd_ms, fwd_ms, bwd_tf, fwd_tf = kernel_rooflines(kt, W.BH, T, d, peaks)
+        out[name] = {"workload": f"B={B} H={H} T={T} d={d} per GPU", "steps": steps, "warmup": 6, "ms_per_step": ms,
+                     "value": value, "unit": UNIT, "frac_of_bf16_peak": value / world / peaks["bf16"],
+                     "frac_of_bf16_sustained_peak": value / world / peaks["bf16_sustained"],
+                     "bwd_kernel": {"launch_ms": bwd_ms, "achieved": bwd_tf, "frac": bwd_tf / peaks["bf16"],
+                                    "timed_launches": kt["bwd_launches"]},
+                     "fwd_kernel": {"kernel": fwd_kernel_name(T, d), "launch_ms": fwd_ms, "achieved": fwd_tf,
+                                    "frac": fwd_tf / peaks["bf16"], "timed_launches": kt["fwd_launches"]},
+                     "l2": f"{W.n_sets} rotating buffer sets", "clocks": clocks}
+        del W
+        torch.cuda.empty_cache()
+        pkg.ops.release()
+    return out
+
+
 def workload_name(args, B, H, T, d):
     return f"{args.workload}: causal attention fwd+bwd, B={B} H={H} T={T} d={d} per GPU, BF16, scale=1/sqrt(d)"
 
@@ -344,9 +459,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemm", default="bf16", choices=["reference", "fp32", "bf16"],
                     help="c4 only: the model's GEMM wrappers - the reference's own FP32 ones, or the drop-in in FP32 / BF16 arithmetic")
-    ap.add_argument("--kernel-event-stride", type=int, default=32,
+    ap.add_argument("--kernel-event-stride", type=int, default=0,
                     help="bracket every N-th launch of each tensor-core kernel with CUDA events inside the timed region "
-                         "(roofline durations); events between kernels undo their back-to-back launch, so N=1 slows the step")
+                         "(roofline durations); events between kernels undo their back-to-back launch, so N=1 slows the "
+                         "step. Default 0 = steps // 8, i.e. about eight sampled launches whatever --steps is")
+    ap.add_argument("--extra", default="c3,c5_512,c5_1024,c5_2048,c5_4096,c5_8192,c5_16384",
+                    help="comma-separated other workloads measured briefly (device-timed) after the main one and reported "
+                         "under `extra`; empty string: none")
     ap.add_argument("--suite", default="attention", choices=["attention", "path-kernels"],
                     help="'path-kernels': time every other launcher of the path (layout, softmax, pre-pass, FP32 parity "
                          "kernels) against the HBM roofline and print one JSON line with a table")
@@ -379,56 +498,15 @@ def main():
     torch.cuda.set_device(dev)
 
     # ---- weak scaling: the global batch is `world` times the per-GPU batch, split by (batch, head) slabs
-    total_slabs = B * H * world
-    mine = pkg.shard.slab_range(total_slabs, rank, world)
-    BH = mine.count
-    n = BH * T * d
-    scale = 1.0 / math.sqrt(d)
-    bf16 = torch.bfloat16
-    set_bytes = 9 * n * 2  # q,k,v,o,dO,dq,dk,dv in BF16 + about one tensor of scratch traffic
-    n_sets = max(2, math.ceil(2.0 * L2_BYTES / set_bytes))  # rotate so that a step's inputs were evicted from L2
-    sets = []
-    for s in range(n_sets):
-        ts = []
-        for i in range(4):  # q, k, v, dO: counter-based streams indexed by global element, distinct per set
-            t = torch.empty(BH, T, d, device=dev, dtype=bf16)
-            ops.fill_normal_(t, seed=1000 + 10 * s + i, offset=pkg.shard.element_offset(mine, T, d))
-            ts.append(t)
-        q, k, v, dO = ts
-        sets.append(dict(q=q, k=k, v=v, dO=dO, o=torch.empty_like(q), lse=torch.empty(BH, T, device=dev),
-                         dq=torch.empty_like(q), dk=torch.empty_like(q), dv=torch.empty_like(q)))
-    ops.reserve(BH, T, d)
-
-    def step(s):
-        ops.attention_forward_bf16(s["q"], s["k"], s["v"], scale, s["o"], s["lse"])
-        ops.attention_backward_bf16(s["q"], s["k"], s["v"], s["o"], s["dO"], s["lse"], scale, s["dq"], s["dk"], s["dv"])
-
+    stride = args.kernel_event_stride if args.kernel_event_stride > 0 else max(1, args.steps // 8)
     sampler = ClockSampler(local) if rank == 0 else None  # started early: nvidia-smi needs a moment to come up
-    for i in range(args.warmup):
-        step(sets[i % n_sets])
-    torch.cuda.synchronize()
-    ops.check_device_fault()
-    if sampler:
-        sampler.wait_first_sample()
-
-    # ---- device-timed region: exactly K steps between barrier + synchronize on both sides
-    ops.kernel_timing(True, every=args.kernel_event_stride)
-    pdist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(sets[i % n_sets])
-    e1.record()
-    torch.cuda.synchronize()
-    pdist.barrier()
-    ms_total = pdist.max_over_ranks(e0.elapsed_time(e1), device=dev)
-    kt = ops.kernel_times()
-    ops.kernel_timing(False)
+    W = DeviceWorkload(pkg, dev, rank, world, B, H, T, d)
+    BH, n, scale, sets, n_sets, set_bytes, step = W.BH, W.n, W.scale, W.sets, W.n_sets, W.set_bytes, W.step
+    ms_total, kt = W.timed_steps(args.steps, args.warmup, stride, sampler)
 
     # ---- the same step replayed from a CUDA graph (the reference's benchmark has such a mode,
     # src/benchmark.cu:158-175): only reported for steps short enough for launch overhead to matter
-    graph_ms = None
+    graph_ms, graphs = None, None
     if ms_total / args.steps < 1.0:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -509,16 +587,56 @@ def main():
     # the last step's results, read on the host: a checksum proves the data made the round trip
     e2e_checksum = float(host_out[(e2e_steps - 1) & 1][0].float().abs().mean())
 
+    # ---- the ceiling of that loop: the same pinned buffers, streams and event chain with no kernel in between.
+    # With N ranks copying at once the host's memory system and the PCIe root complexes are shared, so this is
+    # measured at every N; e2e is then reported as a fraction of it.
+    def copy_only_step(i):
+        b = i & 1
+        st = e2e_sets[b]
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_out[b])
+            for hbuf, key in zip(host_in, ("q", "k", "v", "dO")):
+                st[key].copy_(hbuf, non_blocking=True)
+            ev_in[b].record(s_in)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_in[b])
+            for hbuf, key in zip(host_out[b], ("o", "dq", "dk", "dv")):
+                hbuf.copy_(st[key], non_blocking=True)
+            ev_out[b].record(s_out)
+
+    for i in range(4):
+        copy_only_step(i)
+    torch.cuda.synchronize()
+    pdist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        copy_only_step(i)
+    torch.cuda.synchronize()
+    copy_wall_ms = (time.perf_counter() - t0) * 1e3
+    pdist.barrier()
+    copy_ms = pdist.max_over_ranks(copy_wall_ms, device=dev) / e2e_steps
+
+    # ---- the other benchmark shapes, briefly (every rank takes part: weak scaling like the main workload)
+    peaks = measured_peaks()
+    extra_names = [x for x in args.extra.split(",") if x and x != args.workload]
+    del W, sets, e2e_sets, step, graphs
+    host_in = host_out = None
+    torch.cuda.empty_cache()
+    ops.release()
+    extra = extra_workloads(pkg, dev, rank, world, local, peaks, extra_names) if extra_names else {}
+
     if rank != 0:
         if world > 1:
             torch.distributed.destroy_process_group()
         return
 
-    peaks = measured_peaks()
-    bwd_ms = kt["bwd_ms"] / max(1, kt["bwd_launches"])
-    fwd_ms = kt["fwd_ms"] / max(1, kt["fwd_launches"])
-    bwd_tf = 5.0 * BH * T * T * d / (bwd_ms * 1e-3) / 1e12 if bwd_ms > 0 else 0.0
-    fwd_tf = 2.0 * BH * T * T * d / (fwd_ms * 1e-3) / 1e12 if fwd_ms > 0 else 0.0
+    bwd_ms, fwd_ms, bwd_tf, fwd_tf = kernel_rooflines(kt, BH, T, d, peaks)
+    # algorithmic HBM bytes of one step: BF16 q,k,v read + o written + lse (forward); q,k,v,o,dO read + dq,dk,dv
+    # written + lse (backward) = 24 bytes per element of one tensor, 8 per row
+    step_bytes = 24 * n + 8 * BH * T
+    hbm_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -531,6 +649,10 @@ def main():
         "tokens_per_s": B * world * T / (ms_per_step * 1e-3),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * n * 2, "d2h_bytes_per_step": 4 * n * 2,
                 "ms_per_step": e2e_ms, "steps": e2e_steps, "timing": "host wall clock around the steps, synchronised both sides",
+                "copy_only": {"ms_per_step": copy_ms, "gbs_per_gpu_each_way": 4 * n * 2 / (copy_ms * 1e-3) / 1e9,
+                              "e2e_frac_of_copy_only": copy_ms / e2e_ms,
+                              "note": "the same pinned buffers, streams and events with no kernel in between: the ceiling "
+                                      "the host<->device copy leg sets at this number of GPUs"},
                 "host_result_checksum": e2e_checksum,
                 "path": "pinned host BF16 q,k,v,dO -> device -> b200attn_fwd_bf16 + b200attn_bwd_bf16 -> host o,dq,dk,dv; "
                         "upload, kernels and download of consecutive steps overlap on three streams"},
@@ -539,12 +661,17 @@ def main():
                      "unit": UNIT, "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} (burst cuBLAS BF16)",
                      "traffic": ncu_traffic_per_launch(args.workload), "launch_ms": bwd_ms,
                      "timed_launches": kt["bwd_launches"],
-                     "timing": f"CUDA events around every {args.kernel_event_stride}-th launch inside the timed region",
+                     "timing": f"CUDA events around every {stride}-th launch inside the timed region (mean)",
                      "flops_per_launch": 5.0 * BH * T * T * d,
-                     "forward_kernel": {"kernel": "attn_fwd_tc_kernel", "achieved": fwd_tf, "launch_ms": fwd_ms,
-                                        "frac": fwd_tf / peaks["bf16"]}},
+                     "forward_kernel": {"kernel": fwd_kernel_name(T, d), "achieved": fwd_tf, "launch_ms": fwd_ms,
+                                        "frac": fwd_tf / peaks["bf16"], "timed_launches": kt["fwd_launches"]},
+                     "hbm": {"bound": "hbm", "achieved": hbm_gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                             "frac": hbm_gbs / peaks["hbm"], "bytes_per_step": step_bytes,
+                             "note": "algorithmic bytes of a whole step over ms_per_step: the step is not HBM-bound"}},
         "clocks": clocks,
     }
+    if extra:
+        line["extra"] = extra
     if graph_ms is not None:
         line["cuda_graph_replay"] = {"ms_per_step": graph_ms, "value": all_flops / (graph_ms * 1e-3) / 1e12, "unit": UNIT,
                                      "note": "the same K steps, each buffer set's forward+backward captured once and replayed"}

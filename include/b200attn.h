@@ -52,6 +52,15 @@ int b200attn_release(void);
  * nothing (a device on which no entry point has run yet simply reports 0). */
 int b200attn_check_device_fault(unsigned int* code);
 
+/* Self-test of that chain on a healthy GPU: launches one CTA that waits, with a limit of a few
+ * thousand polls instead of the production 2^22, on a barrier nothing arrives on. The wait gives up,
+ * the kernel ends normally, and the next b200attn_check_device_fault returns
+ * B200ATTN_ERR_DEVICE_FAULT with code 0x57417E57 and clears the word; the context stays usable.
+ * `report` (DEVICE pointer to 2 words, may be NULL) receives the CTA's abort flag and the duration
+ * (in units of 1024 cycles) of a second wait that leaves early because the flag is set.
+ * No reference counterpart (the reference has no waits and checks no launch). */
+int b200attn_selftest_bounded_wait(unsigned int* report, b200attn_stream_t stream);
+
 /* Per-launch timing of the two tensor-core kernels, for roofline reporting: with enable = N > 0,
  * every N-th launch of the forward / backward tcgen05 kernel is bracketed by CUDA events on its
  * stream (N = 1: every launch; an event record between two kernels undoes their programmatic

@@ -45,7 +45,8 @@ def merge(x):
     return x.permute(0, 2, 1, 3).reshape(B, T, H * d).contiguous()
 
 
-CASES = [(2, 300, 3, 64), (1, 1024, 2, 128), (3, 100, 2, 64), (1, 129, 5, 128), (2, 1, 2, 64)]
+# the last case is long enough (d = 128, T > 4096) for the one-CTA-per-SM forward kernel, at a ragged length
+CASES = [(2, 300, 3, 64), (1, 1024, 2, 128), (3, 100, 2, 64), (1, 129, 5, 128), (2, 1, 2, 64), (1, 4200, 2, 128)]
 
 
 @pytest.mark.parametrize("B,T,H,d", CASES)

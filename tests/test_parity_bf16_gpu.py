@@ -115,6 +115,43 @@ def test_long_context_shapes_on_a_slab_subset(ops, BH, T, d, check):
             gate(host(got[sl]), ref[key], f"slab {s} {key}")
 
 
+@pytest.mark.parametrize("BH,T", [(2, 4097), (1, 4224), (2, 5000)])
+def test_long_forward_kernel_at_ragged_lengths(ops, BH, T):
+    """d = 128 beyond T = 4096 runs the one-CTA-per-SM forward (eight softmax warps, three score buffers);
+    lengths that are no multiple of 128 exercise its zero-filled loads and clipped stores. Every slab is
+    compared with the oracle (a T x T FP32 matrix per slab), backward included."""
+    d = 128
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, dO = make_inputs(ops, BH, T, d, seed=3 * T)
+    out, lse = ops.attention_forward_bf16(q, k, v, scale)
+    dq, dk, dv = ops.attention_backward_bf16(q, k, v, out, dO, lse, scale)
+    ops.check_device_fault()
+    for s in range(BH):
+        sl = slice(s, s + 1)
+        ref = orc.attention_forward_backward(host(q[sl]), host(k[sl]), host(v[sl]), host(dO[sl]), scale, dtype=np.float32)
+        assert np.abs(host(lse[sl]) - (ref["m"] + np.log(ref["l"]))).max() <= 1e-3
+        for got, key in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+            gate(host(got[sl]), ref[key], f"T={T} slab {s} {key}")
+
+
+@pytest.mark.parametrize("B,T", [(64, 512), (32, 1024), (16, 2048), (8, 4096)])
+def test_scaling_sweep_shapes_on_a_slab_subset(ops, B, T):
+    """The sweep points H=32, d=128 with T = 512 ... 4096 at their full (B, T): the kernels run on the whole
+    problem (B*32 slabs), the first and the last slab are compared with the oracle."""
+    H, d = 32, 128
+    BH = B * H
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, dO = make_inputs(ops, BH, T, d, seed=31 + T)
+    out, lse = ops.attention_forward_bf16(q, k, v, scale)
+    dq, dk, dv = ops.attention_backward_bf16(q, k, v, out, dO, lse, scale)
+    ops.check_device_fault()
+    for s in (0, BH - 1):
+        sl = slice(s, s + 1)
+        ref = orc.attention_forward_backward(host(q[sl]), host(k[sl]), host(v[sl]), host(dO[sl]), scale, dtype=np.float32)
+        for got, key in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+            gate(host(got[sl]), ref[key], f"B={B} T={T} slab {s} {key}")
+
+
 def test_size_independent_properties_at_full_size(ops):
     """Properties that need no oracle, at config-3 size: V = 1 gives O = 1 (rows of P sum to one);
     the forward is bitwise repeatable; O is linear in V; a (batch, head) shard reproduces the bits of

@@ -337,6 +337,16 @@ extern "C" int b200attn_check_device_fault(unsigned int* code) {
     return B200ATTN_OK;
 }
 
+extern "C" int b200attn_selftest_bounded_wait(unsigned int* report, b200attn_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    DeviceState* st = nullptr;
+    int rc = device_state(stream, &st);
+    if (rc) return rc;
+    if (!st->is_sm100) return fail(B200ATTN_ERR_UNSUPPORTED, "b200attn_selftest_bounded_wait: needs an sm_100a device (B200)");
+    RETURN_IF_CUDA(launch_wait_selftest(st->fault_word, report, stream), "wait self-test launch");
+    return B200ATTN_OK;
+}
+
 extern "C" int b200attn_kernel_timing(int enable) {
     std::lock_guard<std::mutex> lock(g_timed_mutex);
     for (auto& t : g_timed) {

@@ -372,7 +372,6 @@ cudaError_t launch_attn_fwd_tc(const TcFwdArgs& a, cudaStream_t stream) {
     // measured on a B200, forward TFLOP/s: d=64 T=1024 363 vs 248, T=4096 557 vs 462, T=8192 620 vs 524;
     // d=128 T=512 509 vs 352, T=2048 807 vs 716, T=4096 963 vs 930, T=8192 equal.
     if (a.d == 64 || a.T <= 4096) return launch_attn_fwd_tc_short(a, stream);
-    if (a.d == 64) return a.out_is_f32 ? launch_fwd<64, true>(a, stream) : launch_fwd<64, false>(a, stream);
     if (a.d == 128) return a.out_is_f32 ? launch_fwd<128, true>(a, stream) : launch_fwd<128, false>(a, stream);
     return cudaErrorInvalidValue;
 }

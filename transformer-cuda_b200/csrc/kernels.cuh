@@ -124,6 +124,13 @@ cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, lo
 // dq (BF16) = dq_acc (FP32), elementwise.
 cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
 
+// ------------------------------------------------------------------ wait_selftest.cu
+// One CTA waits (with a limit of a few thousand polls) on a barrier nothing arrives on, so that the wait gives up and
+// records kFaultWaitTimeout | kWaitSelfTestId in *fault_word. report (2 words, device memory, may be NULL): the CTA's
+// abort flag and how long a second wait took after the flag was set.
+constexpr unsigned int kWaitSelfTestId = 0x7E57u;
+cudaError_t launch_wait_selftest(unsigned int* fault_word, unsigned int* report, cudaStream_t stream);
+
 // ------------------------------------------------------------------ host-side hooks between api.cu and static_scratch.cu
 // Stores `text` as the calling thread's last error, i.e. what b200attn_last_error() returns (api.cu).
 void set_last_error(const char* text);

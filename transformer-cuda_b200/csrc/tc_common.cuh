@@ -89,15 +89,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 // that gives up; once it is set every later wait returns at once, so a kernel
 // that lost a signal still runs to its end (with wrong data) instead of hanging.
 // The identifier of the wait is recorded in `fault_word` (global memory).
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          unsigned int* fault_word, uint32_t wait_id) {
+__device__ __forceinline__ void mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  unsigned int* fault_word, uint32_t wait_id, uint32_t limit) {
     if (mbar_try_wait(bar, parity)) return;
-    for (uint32_t it = 0; it < B200ATTN_WAIT_LIMIT; ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return;
         if ((it & 1023u) == 1023u && *abort_flag) return;
     }
     *abort_flag = 1u;
     if (fault_word) atomicCAS(fault_word, 0u, kFaultWaitTimeout | (wait_id & 0xffffu));
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          unsigned int* fault_word, uint32_t wait_id) {
+    mbar_wait_limited(bar, parity, abort_flag, fault_word, wait_id, B200ATTN_WAIT_LIMIT);
 }
 
 // --------------------------------- TMA --------------------------------------

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "b200attn_reserve": ([_I, _I, _I], _I),
     "b200attn_release": ([], _I),
     "b200attn_check_device_fault": ([ctypes.POINTER(ctypes.c_uint)], _I),
+    "b200attn_selftest_bounded_wait": ([_P, _P], _I),
     "b200attn_kernel_timing": ([_I], _I),
     "b200attn_kernel_times": ([ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_I), ctypes.POINTER(ctypes.c_double),
                                ctypes.POINTER(_I)], _I),
