@@ -539,6 +539,7 @@ def main():
     # ---- end to end: pinned host buffers -> device -> forward + backward -> host, every step.
     # Every step copies its own inputs in and its own results out; the three legs run on three streams
     # over two device buffer sets, so step i+1's upload and step i-1's download overlap step i's kernels.
+    bf16 = torch.bfloat16
     host_in = [torch.empty(BH, T, d, dtype=bf16).pin_memory() for _ in range(4)]
     for hbuf, key in zip(host_in, ("q", "k", "v", "dO")):
         hbuf.copy_(sets[0][key])
