@@ -4,8 +4,10 @@ pool owns the GPU, or cudaMalloc's implicit synchronisation is not allowed where
 It takes its scratch from a static device array, so it must give what b200attn_bwd_bf16 gives. The
 test calls it through the C ABI twice in a row with different data and shapes - the array keeps the
 previous call's contents, so the second call shows that stale sums are cleared - and compares each
-result with the allocating entry point: dK and dV bit for bit (neither path reorders their sums),
-dQ within the BF16 gates of the other tests (its partial sums are reduced with atomics in both).
+result with the allocating entry point within the BF16 gates of the other tests (max-abs <= 2e-2,
+relative-L2 <= 5e-3): the two entry points may run different kernel variants (at head dim 64 the
+allocating one uses the persistent kernel, whose extra scratch is not part of the static array's
+documented budget), and dQ is reduced with atomics in both.
 After each call the device fault word is polled (the entry point keeps its own word inside the static
 array). A third test checks what the entry point exists for: with the allocating path's scratch released,
 a call leaves the device's free memory where it was. This file sorts last so that a run that stops at the
@@ -36,9 +38,9 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(pkg):
         dq, dk, dv = (torch.full_like(q, float("nan")) for _ in range(3))
         ops.attention_backward_bf16_noalloc(q, k, v, out, dO, lse, scale, dq, dk, dv)
         ops.check_device_fault()  # synchronises; raises if a bounded wait of the no-alloc kernels ran out
-        assert torch.equal(dk, want_dk) and torch.equal(dv, want_dv)
-        m = orc.compute_metrics(dq.float().cpu().numpy(), want_dq.float().cpu().numpy())
-        assert m["max_abs"] <= 2e-2 and m["rel_l2"] <= 5e-3, m
+        for got, want, name in ((dq, want_dq, "dq"), (dk, want_dk, "dk"), (dv, want_dv, "dv")):
+            m = orc.compute_metrics(got.float().cpu().numpy(), want.float().cpu().numpy())
+            assert m["max_abs"] <= 2e-2 and m["rel_l2"] <= 5e-3, (name, m)
 
 
 def test_shapes_beyond_the_static_array_are_rejected(pkg):

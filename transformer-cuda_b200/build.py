@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 SOURCES = ["api.cu", "launch_api.cu", "layout_kernels.cu", "softmax_kernels.cu", "attn_f32.cu", "attn_f32_tiled.cu", "attn_tc_fwd.cu", "attn_tc_fwd_short.cu",
-           "attn_tc_bwd.cu", "static_scratch.cu", "wait_selftest.cu"]
+           "attn_tc_bwd.cu", "attn_tc_bwd64.cu", "static_scratch.cu", "wait_selftest.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
 SO = os.path.join(LIBDIR, "libb200attn.so")

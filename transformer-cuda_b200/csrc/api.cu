@@ -48,7 +48,8 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
     bool ready = false;
     bool is_sm100 = false;
-    unsigned int* fault_word = nullptr;  // device memory, 4 bytes
+    unsigned int* fault_word = nullptr;    // device memory: word 0 of a 64-byte block
+    unsigned int* work_counter = nullptr;  // word 4 of the same block: item counter of the persistent backward
     uint8_t* scratch = nullptr;
     size_t scratch_bytes = 0;
 };
@@ -108,8 +109,9 @@ int device_state(cudaStream_t stream, DeviceState** out) {
         RETURN_IF_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev), "cudaDeviceGetAttribute");
         RETURN_IF_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev), "cudaDeviceGetAttribute");
         st.is_sm100 = (major == 10);
-        RETURN_IF_CUDA(cudaMalloc(&st.fault_word, sizeof(unsigned int)), "cudaMalloc(fault word)");
-        RETURN_IF_CUDA(cudaMemset(st.fault_word, 0, sizeof(unsigned int)), "cudaMemset(fault word)");
+        RETURN_IF_CUDA(cudaMalloc(&st.fault_word, 64), "cudaMalloc(fault word)");
+        RETURN_IF_CUDA(cudaMemset(st.fault_word, 0, 64), "cudaMemset(fault word)");
+        st.work_counter = st.fault_word + 4;
         if (!g_encode) {
             void* fn = nullptr;
             cudaDriverEntryPointQueryResult q;
@@ -147,8 +149,9 @@ int ensure_scratch(DeviceState* st, size_t bytes, cudaStream_t stream) {
 // Scratch demand of the largest consumer (b200attn_bwd_f32 in BF16 mode and b200attn_bwd_bf16).
 size_t scratch_for(long long BH, long long T, long long d) {
     const size_t n = size_t(BH) * T * d, rows = size_t(BH) * T;
-    size_t f32_api = 4 * round_up(n * 2, 256) + round_up(rows * 4, 256);        // bf16 q,k,v,dO + lse2
-    size_t bf16_api = round_up(n * 4, 256) + 2 * round_up(rows * 4, 256);       // dq accumulator + D + lse2
+    const size_t stat_rows = 2 * round_up(rows * 32, 256);                      // lse / D statistics rows (head dim 64)
+    size_t f32_api = 4 * round_up(n * 2, 256) + round_up(rows * 4, 256) + stat_rows;   // bf16 q,k,v,dO + lse2
+    size_t bf16_api = round_up(n * 4, 256) + 2 * round_up(rows * 4, 256) + stat_rows;  // dq accumulator + D + lse2
     return (f32_api > bf16_api ? f32_api : bf16_api) + 256;
 }
 
@@ -186,6 +189,22 @@ int make_map(CUtensorMap* m, const void* base, bool f32, int B, int H, int T, in
                     f32 ? "FP32" : "BF16");
     return B200ATTN_OK;
 }
+
+// (16, T, H, B) view of the dense BF16 (B*H*T, 16) statistics rows: 16 x 128 x 1 x 1 boxes, 32-byte swizzle.
+int make_stat_map(CUtensorMap* m, const void* base, int B, int H, int T) {
+    cuuint64_t dims[4] = {16, cuuint64_t(T), cuuint64_t(H), cuuint64_t(B)};
+    cuuint64_t strides[3] = {32, cuuint64_t(T) * 32, cuuint64_t(H) * T * 32};
+    cuuint32_t box[4] = {16, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (statistics rows, B=%d H=%d T=%d)", int(r), B, H, T);
+    return B200ATTN_OK;
+}
+
+// The persistent head-dim-64 backward folds 1/scale into its statistics rows, so it needs a usable scale.
+bool use_persistent_bwd(int d, float scale) { return d == 64 && scale > 1e-20f && scale < 1e20f; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -233,9 +252,11 @@ int run_fwd_tc(DeviceState* st, const void* q, const void* k, const void* v, voi
 
 // q, k, v share `in_l`, dO uses `do_l`; BF16 dK/dV are written through `grad_l`, FP32 ones as dense (B*H, T, d);
 // the FP32 dQ accumulator is always dense.
+// `ext` holds the statistics rows the pre-pass wrote when use_persistent_bwd(d, scale), null pointers otherwise.
 int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, const void* dO, const float* lse2,
                const float* D, float* dq_acc, void* dk, void* dv, bool grads_f32, int B, int H, int T, int d,
-               const Layout& in_l, const Layout& do_l, const Layout& grad_l, float scale, cudaStream_t stream) {
+               const Layout& in_l, const Layout& do_l, const Layout& grad_l, float scale, cudaStream_t stream,
+               const BwdStatRows& ext) {
     TcBwdArgs a;
     memset(&a, 0, sizeof(a));
     const int BH = B * H;
@@ -259,6 +280,12 @@ int run_bwd_tc(DeviceState* st, const void* q, const void* k, const void* v, con
     a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = st->fault_word;
+    if (ext.lse_ext) {
+        if ((rc = make_stat_map(&a.map_lse_ext, ext.lse_ext, B, H, T))) return rc;
+        if ((rc = make_stat_map(&a.map_d_ext, ext.d_ext, B, H, T))) return rc;
+        a.work_counter = st->work_counter;  // cleared by the pre-pass that precedes this launch in the stream
+    }
+    a.grad_lt = grad_l.t, a.grad_lh = grad_l.h, a.grad_lb = grad_l.b;
     ScopedKernelTimer timer(1, stream);
     RETURN_IF_CUDA(launch_attn_bwd_tc(a, stream), "tensor-core backward launch");
     return B200ATTN_OK;
@@ -514,15 +541,17 @@ extern "C" int b200attn_bwd_f32(const float* q, const float* k, const float* v, 
     __nv_bfloat16* vb = bump.take<__nv_bfloat16>(n);
     __nv_bfloat16* dob = bump.take<__nv_bfloat16>(n);
     float* lse2 = bump.take<float>(size_t(rows));
+    BwdStatRows ext{nullptr, nullptr, 0.f};
+    if (use_persistent_bwd(d, scale)) ext = BwdStatRows{bump.take<__nv_bfloat16>(size_t(rows) * 16), bump.take<__nv_bfloat16>(size_t(rows) * 16), 1.0f / scale};
     RETURN_IF_CUDA(launch_f32_to_bf16(q, qb, (long long)n, stream), "convert q");
     RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
     RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
     RETURN_IF_CUDA(launch_f32_to_bf16(dO, dob, (long long)n, stream), "convert dO");
     // dq is the FP32 accumulator itself: partial sums are reduced straight into the caller's buffer,
     // which the pre-pass clears
-    RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, dq, rows, d, stream), "pre-pass");
+    RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, dq, rows, d, stream, st->work_counter, ext), "pre-pass");
     const Layout sl = slab_layout(BH, T, d);
-    return run_bwd_tc(st, qb, kb, vb, dob, lse2, workspace, dq, dk, dv, true, 1, BH, T, d, sl, sl, sl, scale, stream);
+    return run_bwd_tc(st, qb, kb, vb, dob, lse2, workspace, dq, dk, dv, true, 1, BH, T, d, sl, sl, sl, scale, stream, ext);
 }
 
 extern "C" int b200attn_merge_heads_f32(const float* in, float* out, int B, int H, int T, int d,
@@ -588,12 +617,15 @@ extern "C" int b200attn_bwd_bf16(const void* q, const void* k, const void* v, co
     float* dq_acc = bump.take<float>(n);
     float* D = bump.take<float>(size_t(rows));
     float* lse2 = bump.take<float>(size_t(rows));
+    BwdStatRows ext{nullptr, nullptr, 0.f};
+    if (use_persistent_bwd(d, scale)) ext = BwdStatRows{bump.take<__nv_bfloat16>(size_t(rows) * 16), bump.take<__nv_bfloat16>(size_t(rows) * 16), 1.0f / scale};
     const __nv_bfloat16* ob = static_cast<const __nv_bfloat16*>(o);
     const __nv_bfloat16* dob = static_cast<const __nv_bfloat16*>(dO);
-    RETURN_IF_CUDA(launch_bwd_prepass<__nv_bfloat16>(ob, dob, nullptr, nullptr, lse, D, lse2, dq_acc, rows, d, stream), "pre-pass");
+    RETURN_IF_CUDA(launch_bwd_prepass<__nv_bfloat16>(ob, dob, nullptr, nullptr, lse, D, lse2, dq_acc, rows, d, stream, st->work_counter, ext), "pre-pass");
     const Layout sl = slab_layout(BH, T, d);
-    if ((rc = run_bwd_tc(st, q, k, v, dO, lse2, D, dq_acc, dk, dv, false, 1, BH, T, d, sl, sl, sl, scale, stream))) return rc;
-    RETURN_IF_CUDA(launch_dq_convert(dq_acc, static_cast<__nv_bfloat16*>(dq), (long long)n, stream), "dq convert");
+    if ((rc = run_bwd_tc(st, q, k, v, dO, lse2, D, dq_acc, dk, dv, false, 1, BH, T, d, sl, sl, sl, scale, stream, ext))) return rc;
+    // the persistent kernel leaves the softmax scale out of dS: dK is scaled where it is stored, dQ here
+    RETURN_IF_CUDA(launch_dq_convert(dq_acc, static_cast<__nv_bfloat16*>(dq), (long long)n, stream, ext.lse_ext ? scale : 1.0f), "dq convert");
     return B200ATTN_OK;
 }
 
@@ -639,16 +671,18 @@ extern "C" int b200attn_bwd_bf16_packed(const void* qkv, const void* out, const 
     float* dq_acc = bump.take<float>(n);
     float* D = bump.take<float>(size_t(rows));
     float* lse2 = bump.take<float>(size_t(rows));
+    BwdStatRows ext{nullptr, nullptr, 0.f};
+    if (use_persistent_bwd(d, scale)) ext = BwdStatRows{bump.take<__nv_bfloat16>(size_t(rows) * 16), bump.take<__nv_bfloat16>(size_t(rows) * 16), 1.0f / scale};
     const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(qkv);
     __nv_bfloat16* gb = static_cast<__nv_bfloat16*>(dqkv);
     const size_t C = size_t(H) * d;
     const Layout pl = packed_qkv_layout(H, T, d), ml = merged_layout(H, T, d);
     RETURN_IF_CUDA(launch_bwd_prepass_strided(static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout),
-                                              lse, D, lse2, dq_acc, rows, d, T, H, ml.t, ml.h, ml.b, stream), "pre-pass");
+                                              lse, D, lse2, dq_acc, rows, d, T, H, ml.t, ml.h, ml.b, stream, st->work_counter, ext), "pre-pass");
     if ((rc = run_bwd_tc(st, qb, qb + C, qb + 2 * C, dout, lse2, D, dq_acc, gb + C, gb + 2 * C, false, B, H, T, d, pl, ml, pl,
-                         scale, stream)))
+                         scale, stream, ext)))
         return rc;
-    RETURN_IF_CUDA(launch_dq_convert_strided(dq_acc, gb, rows, d, T, H, pl.t, pl.h, pl.b, stream), "dq convert");
+    RETURN_IF_CUDA(launch_dq_convert_strided(dq_acc, gb, rows, d, T, H, pl.t, pl.h, pl.b, stream, ext.lse_ext ? scale : 1.0f), "dq convert");
     return B200ATTN_OK;
 }
 

@@ -554,6 +554,20 @@ __device__ __forceinline__ float warp_sum(float x) {
     for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
     return x;
 }
+// -x/2 as three BF16 pieces (24 significant bits), twice: the 32-byte statistics row of BwdStatRows
+__device__ __forceinline__ void store_stat_row(__nv_bfloat16* dst_row, float x) {
+    const float v = -0.5f * x;
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+    uint4 w;
+    w.x = uint32_t(__bfloat16_as_ushort(h)) | (uint32_t(__bfloat16_as_ushort(m)) << 16);
+    w.y = uint32_t(__bfloat16_as_ushort(l));
+    w.z = 0u, w.w = 0u;
+    reinterpret_cast<uint4*>(dst_row)[0] = w;
+    reinterpret_cast<uint4*>(dst_row)[1] = w;
+}
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 
@@ -566,12 +580,13 @@ __global__ void __launch_bounds__(256) bwd_prepass_kernel(const TIn* __restrict_
                                                          const float* __restrict__ m, const float* __restrict__ l,
                                                          const float* __restrict__ lse, float* __restrict__ Dout,
                                                          float* __restrict__ lse2, float* __restrict__ zero,
-                                                         long long rows, int d) {
+                                                         long long rows, int d, unsigned int* counter, BwdStatRows ext) {
     constexpr int VEC = 16 / sizeof(TIn);
     pdl_launch_dependents();
     pdl_wait();
     const int tpr = d / VEC;  // threads per row: a power of two <= 32
     const long long gid = blockIdx.x * 256ll + threadIdx.x;
+    if (gid == 0 && counter) *counter = 0u;  // the persistent backward that follows hands out work items from it
     const long long row = gid / tpr;
     const int e = int(gid % tpr) * VEC;
     float acc = 0.f;
@@ -591,7 +606,14 @@ __global__ void __launch_bounds__(256) bwd_prepass_kernel(const TIn* __restrict_
     for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (row < rows && e == 0) {
         Dout[row] = acc;
-        if (lse2) lse2[row] = (lse ? lse[row] : (m[row] + logf(l[row]))) * kLog2e;
+        if (lse2 || ext.lse_ext) {
+            const float lse_nat = lse ? lse[row] : (m[row] + logf(l[row]));
+            if (lse2) lse2[row] = lse_nat * kLog2e;
+            if (ext.lse_ext) {
+                store_stat_row(ext.lse_ext + row * 16, lse_nat * ext.inv_scale);
+                store_stat_row(ext.d_ext + row * 16, acc);
+            }
+        }
     }
 }
 
@@ -602,11 +624,13 @@ __global__ void __launch_bounds__(256) bwd_prepass_strided_kernel(const __nv_bfl
                                                                  const float* __restrict__ lse, float* __restrict__ Dout,
                                                                  float* __restrict__ lse2, float* __restrict__ zero,
                                                                  long long rows, int d, int T, int H, long long lt,
-                                                                 long long lh, long long lb) {
+                                                                 long long lh, long long lb, unsigned int* counter,
+                                                                 BwdStatRows ext) {
     pdl_launch_dependents();
     pdl_wait();
     const int tpr = d / 8;
     const long long gid = blockIdx.x * 256ll + threadIdx.x;
+    if (gid == 0 && counter) *counter = 0u;
     const long long row = gid / tpr;
     const int e = int(gid % tpr) * 8;
     float acc = 0.f;
@@ -628,13 +652,17 @@ __global__ void __launch_bounds__(256) bwd_prepass_strided_kernel(const __nv_bfl
     if (row < rows && e == 0) {
         Dout[row] = acc;
         lse2[row] = lse[row] * kLog2e;
+        if (ext.lse_ext) {
+            store_stat_row(ext.lse_ext + row * 16, lse[row] * ext.inv_scale);
+            store_stat_row(ext.d_ext + row * 16, acc);
+        }
     }
 }
 
 // dQ accumulator (dense FP32 rows) -> BF16 rows addressed through strides; one thread per 8 elements.
 __global__ void __launch_bounds__(256) dq_convert_strided_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
                                                                 long long rows, int d, int T, int H, long long lt,
-                                                                long long lh, long long lb) {
+                                                                long long lh, long long lb, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int tpr = d / 8;
@@ -647,10 +675,10 @@ __global__ void __launch_bounds__(256) dq_convert_strided_kernel(const float* __
     const float4 a0 = __ldg(reinterpret_cast<const float4*>(acc + row * d + e));
     const float4 a1 = __ldg(reinterpret_cast<const float4*>(acc + row * d + e + 4));
     uint4 w;
-    w.x = pack_bf16x2(a0.x, a0.y);
-    w.y = pack_bf16x2(a0.z, a0.w);
-    w.z = pack_bf16x2(a1.x, a1.y);
-    w.w = pack_bf16x2(a1.z, a1.w);
+    w.x = pack_bf16x2(a0.x * scale, a0.y * scale);
+    w.y = pack_bf16x2(a0.z * scale, a0.w * scale);
+    w.z = pack_bf16x2(a1.x * scale, a1.y * scale);
+    w.w = pack_bf16x2(a1.z * scale, a1.w * scale);
     *reinterpret_cast<uint4*>(dq + (bh / H) * lb + (bh % H) * lh + (long long)t * lt + e) = w;
 }
 
@@ -669,6 +697,7 @@ cudaError_t launch_bwd(const TcBwdArgs& a, cudaStream_t stream) {
 
 cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream) {
     if (a.BH == 0 || a.T == 0) return cudaSuccess;
+    if (a.d == 64 && a.work_counter != nullptr) return launch_attn_bwd_tc64(a, stream);
     if (a.d == 64) return a.grads_are_f32 ? launch_bwd<64, true>(a, stream) : launch_bwd<64, false>(a, stream);
     if (a.d == 128) return a.grads_are_f32 ? launch_bwd<128, true>(a, stream) : launch_bwd<128, false>(a, stream);
     return cudaErrorInvalidValue;
@@ -676,43 +705,44 @@ cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream) {
 
 template <typename TIn>
 cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse, float* D,
-                               float* lse2, float* zero, long long rows, int d, cudaStream_t stream) {
+                               float* lse2, float* zero, long long rows, int d, cudaStream_t stream, unsigned int* counter,
+                               BwdStatRows ext) {
     if (rows == 0) return cudaSuccess;
     constexpr int VEC = 16 / sizeof(TIn);
     const int tpr = d / VEC;
     if (d % VEC != 0 || tpr > 32 || (tpr & (tpr - 1)) != 0) return cudaErrorInvalidValue;
     const long long threads = rows * tpr;
     return launch_pdl(bwd_prepass_kernel<TIn>, dim3((unsigned int)((threads + 255) / 256)), dim3(256), 0, stream, o, dO, m, l, lse,
-                      D, lse2, zero, rows, d);
+                      D, lse2, zero, rows, d, counter, ext);
 }
 template cudaError_t launch_bwd_prepass<float>(const float*, const float*, const float*, const float*, const float*,
-                                              float*, float*, float*, long long, int, cudaStream_t);
+                                              float*, float*, float*, long long, int, cudaStream_t, unsigned int*, BwdStatRows);
 template cudaError_t launch_bwd_prepass<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const float*,
                                                       const float*, const float*, float*, float*, float*, long long,
-                                                      int, cudaStream_t);
+                                                      int, cudaStream_t, unsigned int*, BwdStatRows);
 
 cudaError_t launch_bwd_prepass_strided(const __nv_bfloat16* o, const __nv_bfloat16* dO, const float* lse, float* D,
                                        float* lse2, float* zero, long long rows, int d, int T, int H, long long lt,
-                                       long long lh, long long lb, cudaStream_t stream) {
+                                       long long lh, long long lb, cudaStream_t stream, unsigned int* counter, BwdStatRows ext) {
     if (rows == 0) return cudaSuccess;
     const int tpr = d / 8;
     if (d % 8 != 0 || tpr > 32 || (tpr & (tpr - 1)) != 0 || !lse || !lse2 || !zero) return cudaErrorInvalidValue;
     const long long threads = rows * tpr;
     return launch_pdl(bwd_prepass_strided_kernel, dim3((unsigned int)((threads + 255) / 256)), dim3(256), 0, stream, o, dO, lse, D,
-                      lse2, zero, rows, d, T, H, lt, lh, lb);
+                      lse2, zero, rows, d, T, H, lt, lh, lb, counter, ext);
 }
 
 cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, long long rows, int d, int T, int H,
-                                      long long lt, long long lh, long long lb, cudaStream_t stream) {
+                                      long long lt, long long lh, long long lb, cudaStream_t stream, float scale) {
     if (rows == 0) return cudaSuccess;
     if (d % 8 != 0) return cudaErrorInvalidValue;
     const long long threads = rows * (d / 8);
     return launch_pdl(dq_convert_strided_kernel, dim3((unsigned int)((threads + 255) / 256)), dim3(256), 0, stream, dq_acc, dq, rows,
-                      d, T, H, lt, lh, lb);
+                      d, T, H, lt, lh, lb, scale);
 }
 
-cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream) {
-    return launch_f32_to_bf16(dq_acc, dq, n, stream);
+cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream, float scale) {
+    return launch_f32_to_bf16(dq_acc, dq, n, stream, scale);
 }
 
 }  // namespace b200attn

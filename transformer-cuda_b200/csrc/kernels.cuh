@@ -41,7 +41,8 @@ template <typename TIn>
 cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream);
 template <typename TOut>
 cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T, int d, cudaStream_t stream);
-cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream);
+// dst = bf16(src * scale), elementwise
+cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream, float scale = 1.0f);
 cudaError_t launch_fill_normal_f32(float* dst, long long n, unsigned long long seed, long long offset,
                                    cudaStream_t stream);
 cudaError_t launch_fill_normal_bf16(__nv_bfloat16* dst, long long n, unsigned long long seed, long long offset,
@@ -104,25 +105,44 @@ struct TcBwdArgs {
     int tile_major_order;  // 1: CTAs ordered longest tile first across all slabs; 0: slab by slab
     float scale;
     unsigned int* fault_word;
+    // used by the persistent head-dim-64 kernel only
+    unsigned int* work_counter;          // device word, zero at launch: next work item to hand out
+    long long grad_lt, grad_lh, grad_lb; // element strides (row, head, batch) of the BF16 dk / dv tensors
+    CUtensorMap map_lse_ext, map_d_ext;  // BF16 (BH*T, 16) statistics rows written by the pre-pass (see BwdStatRows)
 };
+// Statistics rows for the persistent head-dim-64 kernel: per query row 16 BF16 = two identical 16-byte halves
+// [hi, mid, lo, 0, 0, 0, 0, 0] with hi + mid + lo = -x/2 to 24 significant bits, x = lse/scale (lse_ext) or D (d_ext).
+// One K = 16 MMA step against a tile of ones adds -x to every key row of S^T / dP^T. Both pointers null: not written.
+struct BwdStatRows {
+    __nv_bfloat16* lse_ext;
+    __nv_bfloat16* d_ext;
+    float inv_scale;  // 1 / softmax scale
+};
+// d = 128, and d = 64 when a.work_counter is NULL: one CTA per key tile. d = 64 with a work counter: the persistent
+// kernel of attn_tc_bwd64.cu.
 cudaError_t launch_attn_bwd_tc(const TcBwdArgs& a, cudaStream_t stream);
+cudaError_t launch_attn_bwd_tc64(const TcBwdArgs& a, cudaStream_t stream);
 
 // Backward pre-pass: D = rowsum(dO*O) and lse2 = (m + log l) * log2(e) or lse * log2(e).
 // TIn is float or __nv_bfloat16. Exactly one of (m,l) / lse is given. If `zero` is not null the
 // pass also clears that (rows, d) FP32 buffer (the dQ accumulator). d/VEC (VEC = 16 bytes of TIn)
-// must be a power of two <= 32.
+// must be a power of two <= 32. If `counter` is not null the pass also clears that word (the work counter of the
+// persistent backward kernel that follows it in the stream).
 template <typename TIn>
 cudaError_t launch_bwd_prepass(const TIn* o, const TIn* dO, const float* m, const float* l, const float* lse,
-                               float* D, float* lse2, float* zero, long long rows, int d, cudaStream_t stream);
+                               float* D, float* lse2, float* zero, long long rows, int d, cudaStream_t stream,
+                               unsigned int* counter = nullptr, BwdStatRows ext = BwdStatRows{nullptr, nullptr, 0.f});
 // The same for BF16 O / dO rows addressed as base + b*lb + h*lh + t*lt (+ e), row = (b*H + h)*T + t; lse given.
 cudaError_t launch_bwd_prepass_strided(const __nv_bfloat16* o, const __nv_bfloat16* dO, const float* lse, float* D,
                                        float* lse2, float* zero, long long rows, int d, int T, int H, long long lt,
-                                       long long lh, long long lb, cudaStream_t stream);
-// dq (BF16, rows addressed as above) = dq_acc (FP32, dense rows).
+                                       long long lh, long long lb, cudaStream_t stream, unsigned int* counter = nullptr,
+                                       BwdStatRows ext = BwdStatRows{nullptr, nullptr, 0.f});
+// dq (BF16, rows addressed as above) = dq_acc (FP32, dense rows) * scale. The persistent head-dim-64 kernel leaves the
+// softmax scale out of dS, so its dQ sums are scaled here; the other kernels pass 1.
 cudaError_t launch_dq_convert_strided(const float* dq_acc, __nv_bfloat16* dq, long long rows, int d, int T, int H,
-                                      long long lt, long long lh, long long lb, cudaStream_t stream);
-// dq (BF16) = dq_acc (FP32), elementwise.
-cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream);
+                                      long long lt, long long lh, long long lb, cudaStream_t stream, float scale = 1.0f);
+// dq (BF16) = dq_acc (FP32) * scale, elementwise.
+cudaError_t launch_dq_convert(const float* dq_acc, __nv_bfloat16* dq, long long n, cudaStream_t stream, float scale = 1.0f);
 
 // ------------------------------------------------------------------ wait_selftest.cu
 // One CTA waits (with a limit of a few thousand polls) on a barrier nothing arrives on, so that the wait gives up and

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kThreads) head_transpose_kernel(const THead* _
 
 __global__ void __launch_bounds__(kThreads) f32_to_bf16_kernel(const float* __restrict__ src,
                                                               __nv_bfloat16* __restrict__ dst, long long n8,
-                                                              long long n) {
+                                                              long long n, float scale) {
     // the last kernel of the BF16 backward chain: launched with programmatic serialisation (see launch_pdl)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -178,10 +178,12 @@ __global__ void __launch_bounds__(kThreads) f32_to_bf16_kernel(const float* __re
     if (g < n8) {
         float a[8];
         load_as_f32<8>(src + g * 8, a);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) a[x] *= scale;  // exact no-op for scale = 1
         store_from_f32<8>(dst + g * 8, a);
     } else {
         long long i = n8 * 8 + (g - n8);
-        if (i < n) dst[i] = __float2bfloat16_rn(src[i]);
+        if (i < n) dst[i] = __float2bfloat16_rn(src[i] * scale);
     }
 }
 
@@ -291,12 +293,12 @@ cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T
 template cudaError_t launch_split_heads<float>(const float*, float*, int, int, int, int, cudaStream_t);
 template cudaError_t launch_split_heads<__nv_bfloat16>(const float*, __nv_bfloat16*, int, int, int, int, cudaStream_t);
 
-cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream) {
+cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream, float scale) {
     if (n == 0) return cudaSuccess;
     bool vec_ok = aligned16(src) && aligned16(dst);
     long long n8 = vec_ok ? n / 8 : 0;
     long long work = n8 + (n - n8 * 8);
-    return launch_pdl(f32_to_bf16_kernel, dim3(blocks_for(work)), dim3(kThreads), 0, stream, src, dst, n8, n);
+    return launch_pdl(f32_to_bf16_kernel, dim3(blocks_for(work)), dim3(kThreads), 0, stream, src, dst, n8, n, scale);
 }
 
 cudaError_t launch_fill_normal_f32(float* dst, long long n, unsigned long long seed, long long offset,

@@ -196,6 +196,7 @@ extern "C" int b200attn_bwd_bf16_noalloc(const void* q, const void* k, const voi
     a.tile_major_order = (size_t(BH) * T * d * 2 * 4 <= (size_t(64) << 20)) ? 1 : 0;  // Q,K,V,dO fit in half of L2
     a.scale = scale;
     a.fault_word = fault_word;
+    a.work_counter = nullptr;  // one CTA per key tile: the kernel variant whose scratch is what the header documents
 
     cudaError_t e = launch_bwd_prepass<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dO),
                                                       nullptr, nullptr, lse, D, lse2, nullptr, (long long)rows, d, stream);

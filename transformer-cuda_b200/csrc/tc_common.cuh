@@ -104,6 +104,36 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
     mbar_wait_limited(bar, parity, abort_flag, fault_word, wait_id, B200ATTN_WAIT_LIMIT);
 }
 
+// The same bounded wait with its polling loop OUT OF LINE (one copy per kernel instead of one per wait: a kernel
+// with dozens of waits and several warp roles otherwise carries some 20 KB of polling code, and instruction-cache
+// misses - not arithmetic - then pace its single-warp roles). `sleep_ns` > 0: the warp sleeps between polls, so
+// that a role that expects to wait long does not compete for issue slots with the warps that have work.
+static __device__ __noinline__ void mbar_wait_poll(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag,
+                                            unsigned int* fault_word, uint32_t wait_id, uint32_t sleep_ns) {
+    for (uint32_t it = 0; it < B200ATTN_WAIT_LIMIT; ++it) {
+        if (sleep_ns) __nanosleep(sleep_ns);
+        uint32_t ok;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, P;\n\t"
+            "}\n"
+            : "=r"(ok)
+            : "r"(bar_addr), "r"(parity)
+            : "memory");
+        if (ok) return;
+        if ((it & 1023u) == 1023u && *abort_flag) return;
+    }
+    *abort_flag = 1u;
+    if (fault_word) atomicCAS(fault_word, 0u, kFaultWaitTimeout | (wait_id & 0xffffu));
+}
+__device__ __forceinline__ void mbar_wait_compact(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  unsigned int* fault_word, uint32_t wait_id, uint32_t sleep_ns) {
+    if (mbar_try_wait(bar, parity)) return;
+    mbar_wait_poll(smem_u32(bar), parity, abort_flag, fault_word, wait_id, sleep_ns);
+}
+
 // --------------------------------- TMA --------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -319,6 +349,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return r;
 }
 
+// Elementwise product of two packed bf16x2 words.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -358,6 +395,22 @@ __device__ __forceinline__ float mixed_exp2(float x, int e) {
 // Named barrier over a subset of the CTA's warps (id 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// The same barrier returning the OR of `pred` over all participating threads (identical in every one of them).
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t nthreads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(r)
+        : "r"(id), "r"(nthreads), "r"(uint32_t(pred))
+        : "memory");
+    return r != 0;
 }
 
 // Vector reduction into global FP32 memory (16-byte aligned address).
