@@ -168,8 +168,8 @@ def run_reference(args, B, H, T, d):
 def run_gpt_step(args):
     """Config 4: full synthetic GPT training step (L=12, C=768, H=12, d_ff=3072, V=50257, T=1024, per-GPU B=16,
     AdamW), data-parallel with one NCCL all-reduce of the gradient buffer per step. The step is the reference's
-    own model code linked against this engine (transformer-cuda_b200/harness/gpt_step_dp.cu; binary prebuilt by
-    oracle/Makefile where the reference checkout exists). Launched by torchrun, every bench.py rank starts the
+    own model code linked against this engine (transformer-cuda_b200/harness/gpt_step_dp.cu; binary prebuilt into
+    build/ by transformer-cuda_b200/harness/Makefile where the reference checkout exists). Launched by torchrun, every bench.py rank starts the
     binary as its rank's process (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_PORT are inherited); rank 0 relays the
     JSON line. `--impl reference` runs the same harness linked against the reference's own attention kernels."""
     rank = int(os.environ.get("RANK", "0"))
@@ -180,11 +180,11 @@ def run_gpt_step(args):
         name = "gpt_step_dp_ref"
     else:
         name = "gpt_step_dp_b200" if args.gemm == "reference" else "gpt_step_dp_b200_gemm"
-    exe = os.path.join(ROOT, "oracle", "_ref", name)
+    exe = os.path.join(ROOT, "build", name)
     if not os.path.exists(exe):
         if rank == 0:
             print(json.dumps({"impl": args.impl, "metric": "gpt_step_tokens_per_s",
-                              "unavailable": f"{name} is built from the reference checkout by `make -C oracle`; not present here"}))
+                              "unavailable": f"build/{name} is built by transformer-cuda_b200/harness/Makefile where a reference checkout exists; not present here"}))
         return
     steps = max(1, min(args.steps, 20))
     env = dict(os.environ)

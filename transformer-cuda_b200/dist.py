@@ -69,3 +69,16 @@ def gather_slabs(local: torch.Tensor, total_slabs: int) -> torch.Tensor:
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded)
     return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
+
+
+def average_gradients_(flat_grads: torch.Tensor) -> torch.Tensor:
+    """The gradient exchange of the data-parallel training step (config 4), in place on one flat buffer: sum over
+    ranks, then multiply by 1/world (what ncclAllReduce(avg) does in transformer-cuda_b200/harness/gpt_step_dp.cu).
+    It runs once per step on the finished buffer, before the optimizer: the reference's fused_step computes the
+    global gradient norm and clears the buffer (src/optimizer.cu:225-249), so every rank must see the averaged
+    gradient first. Every rank then applies the identical update and the replicas stay bit-identical."""
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(flat_grads, op=dist.ReduceOp.SUM)
+        flat_grads.mul_(1.0 / dist.get_world_size())
+    return flat_grads
+

@@ -7,8 +7,10 @@
 // object the binary is linked against: libb200attn (this engine) or the reference's own
 // src/kernels/attention.cu (the "reference kernels on the same GPU" arm). Per step:
 //
-//     forward -> backward -> ncclAllReduce(sum) of the contiguous gradient buffer over NVLink
-//             -> gradients * 1/world -> AdamW::fused_step (global-norm clip + AdamW + zero-grad)
+//     forward -> backward -> ncclAllReduce(avg) of the contiguous gradient buffer over NVLink
+//             -> AdamW::fused_step (global-norm clip + AdamW + zero-grad)
+//
+// The mean over ranks is taken inside the collective (ncclAvg), so no separate pass scales the 163 M-float buffer.
 //
 // The all-reduce runs once per step on the finished buffer, before fused_step, because the
 // reference accumulates bias / LayerNorm / embedding gradients with atomics into a buffer that
@@ -44,11 +46,6 @@
             exit(2);                                                                        \
         }                                                                                   \
     } while (0)
-
-__global__ void scale_kernel(float* __restrict__ x, size_t n, float s) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t j = blockIdx.x * (size_t)blockDim.x + threadIdx.x; j < n; j += stride) x[j] *= s;
-}
 
 static int env_int(const char* name, int dflt) {
     const char* s = getenv(name);
@@ -140,12 +137,25 @@ int main(int argc, char** argv) {
     CUDA_CHECK(cudaMalloc(&d_time, sizeof(float)));
     float host_loss = 0.f;
 
+    // events around every all-reduce of the timed steps: the collective's share of a step is reported
+    std::vector<cudaEvent_t> ar_events;
+    bool time_allreduce = false;
     auto step = [&](float* loss) {
         model.forward(d_tok, stream);
         model.backward(d_tok, d_tgt, loss, stream);
         if (world > 1) {
-            NCCL_CHECK(ncclAllReduce(model.get_grads_memory(), model.get_grads_memory(), n_params, ncclFloat, ncclSum, comm, stream));
-            scale_kernel<<<1184, 256, 0, stream>>>(model.get_grads_memory(), n_params, 1.0f / world);
+            cudaEvent_t a0 = nullptr, a1 = nullptr;
+            if (time_allreduce) {
+                CUDA_CHECK(cudaEventCreate(&a0));
+                CUDA_CHECK(cudaEventCreate(&a1));
+                CUDA_CHECK(cudaEventRecord(a0, stream));
+            }
+            NCCL_CHECK(ncclAllReduce(model.get_grads_memory(), model.get_grads_memory(), n_params, ncclFloat, ncclAvg, comm, stream));
+            if (time_allreduce) {
+                CUDA_CHECK(cudaEventRecord(a1, stream));
+                ar_events.push_back(a0);
+                ar_events.push_back(a1);
+            }
         }
         optimizer.fused_step(cfg.learning_rate, cfg.grad_clip, stream);
     };
@@ -159,6 +169,7 @@ int main(int argc, char** argv) {
     cudaEvent_t e0, e1;
     CUDA_CHECK(cudaEventCreate(&e0));
     CUDA_CHECK(cudaEventCreate(&e1));
+    time_allreduce = true;
     CUDA_CHECK(cudaEventRecord(e0, stream));
     for (int i = 0; i < steps; ++i) step(i == steps - 1 ? &host_loss : nullptr);
     CUDA_CHECK(cudaEventRecord(e1, stream));
@@ -171,6 +182,12 @@ int main(int argc, char** argv) {
         CUDA_CHECK(cudaStreamSynchronize(stream));
         CUDA_CHECK(cudaMemcpy(&ms, d_time, sizeof(float), cudaMemcpyDeviceToHost));
     }
+    double ar_ms = 0.0;
+    for (size_t i = 0; i + 1 < ar_events.size(); i += 2) {
+        float t = 0.f;
+        CUDA_CHECK(cudaEventElapsedTime(&t, ar_events[i], ar_events[i + 1]));
+        ar_ms += t;
+    }
     if (rank == 0) {
         const double ms_step = ms / steps;
 #ifdef B200ATTN_DROPIN
@@ -179,10 +196,10 @@ int main(int argc, char** argv) {
         const char* attn = "reference src/kernels/attention.cu";
 #endif
         printf("{\"metric\": \"gpt_step_tokens_per_s\", \"value\": %.1f, \"unit\": \"tokens/s\", \"n_gpus\": %d, \"steps\": %d, "
-               "\"warmup\": %d, \"ms_per_step\": %.3f, \"loss\": %.5f, \"attention\": \"%s\", \"params\": %zu, "
+               "\"warmup\": %d, \"ms_per_step\": %.3f, \"allreduce_ms_per_step\": %.3f, \"loss\": %.5f, \"attention\": \"%s\", \"params\": %zu, "
                "\"config\": {\"L\": %zu, \"C\": %zu, \"H\": %zu, \"d_ff\": %zu, \"V\": %zu, \"T\": %d, \"per_gpu_batch\": %d, "
-               "\"optimizer\": \"AdamW lr=3e-4 betas=(0.9,0.95) wd=0.1 clip=1.0\", \"parallelism\": \"dp%d, one ncclAllReduce of the gradient buffer per step\"}}\n",
-               (double)world * B * T / (ms_step * 1e-3), world, steps, warmup, ms_step, host_loss, attn, n_params,
+               "\"optimizer\": \"AdamW lr=3e-4 betas=(0.9,0.95) wd=0.1 clip=1.0\", \"parallelism\": \"dp%d, one ncclAllReduce(avg) of the gradient buffer per step\"}}\n",
+               (double)world * B * T / (ms_step * 1e-3), world, steps, warmup, ms_step, ar_ms / steps, host_loss, attn, n_params,
                cfg.num_layers, cfg.d_model, cfg.num_heads, cfg.d_ff, cfg.vocab_size, T, B, world);
     }
     if (comm) ncclCommDestroy(comm);
