@@ -210,6 +210,18 @@ def run_gpt_step(args):
             "loss_after_last_step": child["loss"],
             "allreduce_ms_per_step": child.get("allreduce_ms_per_step"),
             "allreduce": "one in-place ncclAllReduce(avg) of the 163 M-float gradient buffer per step, timed with CUDA events on rank 0"}
+    if world == 1 and args.impl != "reference" and not args.no_cpu_baseline:
+        # the reference's PyTorch twin of the whole step on the host cores (a port: the checkout is not on this machine)
+        import torch
+        from oracle import torch_gpt_port
+        torch.set_num_threads(os.cpu_count() or 1)
+        c = child["config"]
+        r = torch_gpt_port.time_training_step(c["V"], c["T"], c["C"], c["L"], c["H"], batch=1, steps=1)
+        line["cpu_baseline"] = {"value": r["tokens_per_step"] / r["seconds_per_step"], "unit": "tokens/s", "cores": r["threads"],
+                                "kind": "port",
+                                "sample": f"one un-warmed training step (forward, autograd backward, clip, AdamW) on 1 of the "
+                                          f"{c['per_gpu_batch']} rows of the per-GPU batch ({r['tokens_per_step']} tokens), "
+                                          f"{r['seconds_per_step']:.1f} s, PyTorch FP32"}
     print(json.dumps(line), flush=True)
 
 

@@ -6,7 +6,9 @@ import math
 import numpy as np
 import pytest
 
-from conftest import golden_names, load_golden
+import os
+
+from conftest import GOLDEN_DIR, golden_names, load_golden
 from oracle import attention_oracle as orc
 
 TOL = 1e-5  # the FP32 parity gate of the path (max-abs)
@@ -103,3 +105,24 @@ def test_torch_port_agrees_with_numpy_oracle():
     ref = orc.attention_forward_backward(q, k, v, dO, scale)
     for got, key in ((out, "out"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
         assert orc.compute_metrics(got.numpy(), ref[key])["max_abs"] <= TOL, key
+
+
+@pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])
+def test_gpt_port_matches_the_reference_generator(case):
+    """oracle/torch_gpt_port.py (the CPU baseline of the full training step) against the files the reference's own
+    golden generator wrote from PyTorchGPT (pytorch_src/utils.py:167-240): logits, loss and the flat gradient in the
+    CUDA blob order, at the gates of scripts/compare_parity.py:108-117."""
+    import torch
+    from oracle import torch_gpt_port as gpt
+    d = os.path.join(GOLDEN_DIR, case)
+    B, T, C, L, H, V = (int(x) for x in open(os.path.join(d, "config.txt")).read().split())
+    load = lambda n, dt=np.float32: np.fromfile(os.path.join(d, n), dtype=dt)
+    flat = torch.from_numpy(load("pytorch_params.bin")).clone().requires_grad_(True)
+    assert flat.numel() == gpt.num_parameters(V, T, C, L)
+    idx = torch.from_numpy(load("inputs.bin", np.int32).astype(np.int64)).view(B, T)
+    tgt = torch.from_numpy(load("targets.bin", np.int32).astype(np.int64)).view(B, T)
+    logits, loss = gpt.gpt_forward(flat, idx, tgt, V, T, C, L, H)
+    loss.backward()
+    assert np.abs(logits.detach().numpy().ravel() - load("pytorch_logits.bin")).max() <= 1e-5
+    assert abs(float(loss) - float(load("pytorch_loss.bin")[0])) <= 1e-5
+    assert np.abs(flat.grad.numpy() - load("pytorch_grads.bin")).max() <= 5e-5

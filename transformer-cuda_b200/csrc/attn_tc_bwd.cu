@@ -30,39 +30,6 @@
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
-#ifdef B200ATTN_TRACE
-// Debug builds only: clock64() stamps of the first CTA's MMA warp and compute thread 0, read back by
-// b200attn_debug_read_bwd_trace(). Slot = role * 2048 + iteration * 16 + point (role 2: compute thread 255).
-__device__ long long g_bwd_trace[6144];
-#define BWD_TRACE(role, it, point)                                                              \
-    do {                                                                                        \
-        if (blockIdx.x == 0 && (it) < 128) g_bwd_trace[(role) * 2048 + (it) * 16 + (point)] = clock64(); \
-    } while (0)
-extern "C" int b200attn_debug_read_bwd_trace(long long* host, int count) {
-    return (int)cudaMemcpyFromSymbol(host, g_bwd_trace, sizeof(long long) * (size_t)count);
-}
-// Per-CTA life line: {globaltimer at start, after prologue (first S^T ready), at loop end, at exit, smid, iterations}.
-__device__ long long g_bwd_cta_trace[8 * 4096];
-extern "C" int b200attn_debug_read_bwd_cta_trace(long long* host, int count) {
-    return (int)cudaMemcpyFromSymbol(host, g_bwd_cta_trace, sizeof(long long) * (size_t)count);
-}
-__device__ __forceinline__ long long b200attn_globaltimer() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define BWD_CTA_TRACE(slot, value)                                                            \
-    do {                                                                                      \
-        if (blockIdx.x < 4096) g_bwd_cta_trace[blockIdx.x * 8 + (slot)] = (value);            \
-    } while (0)
-#else
-#define BWD_TRACE(role, it, point) \
-    do {                           \
-    } while (0)
-#define BWD_CTA_TRACE(slot, value) \
-    do {                           \
-    } while (0)
-#endif
 
 namespace b200attn {
 namespace {
@@ -131,15 +98,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     const int jt = a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_tiles);
     const int hh = bh % a.H, bb = bh / a.H;  // head and batch coordinates of the 4-D tensor maps
     const int n_it = n_tiles - jt;        // query tiles jt .. n_tiles-1
-#ifdef B200ATTN_TRACE
-    if (threadIdx.x == 0) {
-        unsigned int smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        BWD_CTA_TRACE(0, b200attn_globaltimer());
-        BWD_CTA_TRACE(4, (long long)smid);
-        BWD_CTA_TRACE(5, (long long)n_it);
-    }
-#endif
 
     if (tid == 0) {
         mbar_init(&bars.k_full, 1);
@@ -256,7 +214,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             // dV += P^T dO
             mbar_wait(&bars.p_ready, it & 1, &abort_flag, a.fault_word, 0x55);
             tc_fence_after();
-            if (lane == 0) BWD_TRACE(0, it, 0);
             if (elect_one()) {
                 const uint64_t do_mnmaj = make_smem_desc_sw128(smem_u32(sDO + os * Cfg::kTileBytes), kAtomBytes, 1024);
 #pragma unroll
@@ -266,12 +223,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 tc_commit(&bars.do_empty[os]);  // dP^T(it) and dV(it) were the readers of this dO tile
             }
             __syncwarp();
-            if (lane == 0) BWD_TRACE(0, it, 1);
             if (it + 1 < n_it) issue_st(it + 1);  // overlaps the exponentials of the next tile with dK/dQ of this one
-            if (lane == 0) BWD_TRACE(0, it, 2);
             // dK += dS^T Q ; dQ = dS K
             mbar_wait(&bars.ds_ready, it & 1, &abort_flag, a.fault_word, 0x56);
-            if (lane == 0) BWD_TRACE(0, it, 3);
             // dS^T(it) done means dP^T(it) has been consumed: with dQ in its own columns the next dP^T can go first
             if (!Cfg::kDqAliased && it + 1 < n_it) issue_dp(it + 1);
             tc_fence_after();
@@ -298,9 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 tc_commit(&bars.dq_full);
             }
             __syncwarp();
-            if (lane == 0) BWD_TRACE(0, it, 4);
             if (Cfg::kDqAliased && it + 1 < n_it) issue_dp(it + 1);
-            if (lane == 0) BWD_TRACE(0, it, 5);
         }
     } else {
         // ------------------------------------------------------------ compute warps: thread (r, half) =
@@ -323,18 +275,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
         auto dq_fetch = [&](int it) {  // TMEM -> registers; frees the dQ columns for the MMA warp
             mbar_wait(&bars.dq_full, it & 1, &abort_flag, a.fault_word, 0x60);
             tc_fence_after();
-            if (tid == 0) BWD_TRACE(1, it + 1, 11);
 #pragma unroll
             for (int c = 0; c < D / 2; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColDQ + half * (D / 2) + c), &dqv[c]);
             tmem_wait_ld();
-            if (tid == 0) BWD_TRACE(1, it + 1, 12);
             tc_fence_before();
             mbar_arrive(&bars.dq_empty);
         };
         auto dq_send = [&](int it, int rd) {  // registers -> staging -> reduce-add, 32 columns per thread
             if (tid == 0) tma_store_wait_read();  // earlier reductions have finished reading the staging tile
             named_bar_sync(2, kComputeThreads);
-            if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 13);
             uint8_t* stage = sDQ + half * kAtomBytes;
 #pragma unroll
             for (int x = 0; x < 32; x += 4)
@@ -342,7 +291,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                     make_uint4(dqv[rd * 32 + x], dqv[rd * 32 + x + 1], dqv[rd * 32 + x + 2], dqv[rd * 32 + x + 3]);
             fence_proxy_async_smem();
             named_bar_sync(2, kComputeThreads);
-            if (tid == 0 && rd == 0) BWD_TRACE(1, it + 1, 14);
             if (tid == 0) {
                 tma_reduce_add_4d(&a.map_dq_acc, sDQ, rd * 32, (jt + it) * kBQ, hh, bb);
                 tma_reduce_add_4d(&a.map_dq_acc, sDQ + kAtomBytes, D / 2 + rd * 32, (jt + it) * kBQ, hh, bb);
@@ -371,17 +319,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
         for (int it = 0; it < n_it; ++it) {
             const int i = jt + it;
             const int buf = it & 1;
-            if (tid == 0) BWD_TRACE(1, it, 0);
-            if (tid == 255) BWD_TRACE(2, it, 0);
 
             // ---- P^T
-            if (tid == 0) BWD_TRACE(1, it, 1);
             mbar_wait(&bars.s_full, it & 1, &abort_flag, a.fault_word, 0x61);
             tc_fence_after();
-            if (tid == 0) BWD_TRACE(1, it, 2);
-#ifdef B200ATTN_TRACE
-            if (tid == 0 && it == 0) BWD_CTA_TRACE(1, b200attn_globaltimer());
-#endif
             float p[kBQ / 2];
             const bool diag = (i == jt);
 #pragma unroll
@@ -390,7 +331,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 uint32_t sv[32];
                 tmem_ld32(tmem_addr(tmem, lane_base, Cfg::kColS + c), sv);
                 tmem_wait_ld();
-                if (tid == 0 && cc == 0) BWD_TRACE(1, it, 7);
                 uint32_t pk[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 4) {
@@ -407,16 +347,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 }
                 // each half packs its P^T into the first 32 columns of its OWN 64 score columns, so the
                 // other half's unread scores are never overwritten
-                if (tid == 0 && cc == 0) BWD_TRACE(1, it, 8);
                 tmem_st16(tmem_addr(tmem, lane_base, Cfg::kColS + c_begin + (cc >> 1)), pk);
             }
-            if (tid == 0) BWD_TRACE(1, it, 9);
             tmem_wait_st();
-            if (tid == 0) BWD_TRACE(1, it, 10);
             tc_fence_before();
             mbar_arrive(&bars.p_ready);
-            if (tid == 0) BWD_TRACE(1, it, 3);
-            if (tid == 255) BWD_TRACE(2, it, 3);
 
             // ---- d = 128: the previous tile's dQ partial sits in the dP^T columns and has to leave before
             // dP^T of this tile can be produced (its MMA ran while the exponentials above were computed)
@@ -424,8 +359,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 dq_fetch(it - 1);
                 dq_send(it - 1, 0);
             }
-            if (tid == 0) BWD_TRACE(1, it, 4);
-            if (tid == 255) BWD_TRACE(2, it, 4);
 
             // ---- dS^T
             mbar_wait(&bars.dp_full, it & 1, &abort_flag, a.fault_word, 0x62);
@@ -433,8 +366,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             // commit behind that dQ has arrived (at d = 128 the drain above has already waited for it)
             if (!Cfg::kDqAliased && it > 0) mbar_wait(&bars.dq_full, (it - 1) & 1, &abort_flag, a.fault_word, 0x66);
             tc_fence_after();
-            if (tid == 0) BWD_TRACE(1, it, 5);
-            if (tid == 255) BWD_TRACE(2, it, 5);
             {
                 // both TMEM loads and the statistics are requested before the single wait: chunk-by-chunk
                 // (load, wait, compute, store) exposed the load latency twice and measured 860 cycles
@@ -466,8 +397,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(&bars.ds_ready);
-            if (tid == 0) BWD_TRACE(1, it, 6);
-            if (tid == 255) BWD_TRACE(2, it, 6);
             // ---- statistics of the next tile, then the (rest of the) previous tile's dQ partial; the
             // barrier inside dq_send (or the explicit one on the first step) publishes the statistics
             if (it + 1 < n_it) {
@@ -483,9 +412,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
                 dq_send(it - 1, 0);
             }
         }
-#ifdef B200ATTN_TRACE
-        if (tid == 0) BWD_CTA_TRACE(2, b200attn_globaltimer());
-#endif
         dq_fetch(n_it - 1);  // dq_full of the last tile also means every dV / dK MMA has retired
         dq_send(n_it - 1, 0);
         if (Cfg::kDqRounds == 2) dq_send(n_it - 1, 1);
@@ -543,9 +469,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc_kernel(const __grid_c
     tc_fence_before();
     __syncthreads();
     if (warp == kProducerWarp) tmem_dealloc(tmem, Cfg::kTmemCols);
-#ifdef B200ATTN_TRACE
-    if (threadIdx.x == 0) BWD_CTA_TRACE(3, b200attn_globaltimer());
-#endif
 }
 
 // ------------------------------------------------------------------ pre-pass

@@ -28,22 +28,6 @@
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
-#ifdef B200ATTN_TRACE
-// Debug builds only: clock64() stamps of the first CTA's MMA warp and softmax thread 0.
-// Slot = role * 2048 + tile * 16 + point.
-__device__ long long g_fwd_trace[4096];
-#define FWD_TRACE(role, j, point)                                                              \
-    do {                                                                                       \
-        if (blockIdx.x == 0 && (j) < 128) g_fwd_trace[(role) * 2048 + (j) * 16 + (point)] = clock64(); \
-    } while (0)
-extern "C" int b200attn_debug_read_fwd_trace(long long* host, int count) {
-    return (int)cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(long long) * (size_t)count);
-}
-#else
-#define FWD_TRACE(role, j, point) \
-    do {                          \
-    } while (0)
-#endif
 
 namespace b200attn {
 namespace {
@@ -167,7 +151,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             const int ks = j % Cfg::kKStages;
             mbar_wait(&bars.k_full[ks], (j / Cfg::kKStages) & 1, &abort_flag, a.fault_word, 0x21);
             tc_fence_after();
-            if (lane == 0) FWD_TRACE(0, j, 0);
             if (elect_one()) {
                 const uint64_t k_desc = make_smem_desc_sw128(smem_u32(sK + ks * Cfg::kTileBytes), 0, 1024);
                 const uint32_t d_tmem = tmem + Cfg::kColS + (j % Cfg::kSBuffers) * 128;
@@ -180,7 +163,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
                 tc_commit(&bars.s_full[j % Cfg::kSBuffers]);
             }
             __syncwarp();
-            if (lane == 0) FWD_TRACE(0, j, 1);
         };
         issue_qk(0);
         if (n_kv > 1) issue_qk(1);
@@ -192,7 +174,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             mbar_wait(&bars.v_full[vs], (j / Cfg::kVStages) & 1, &abort_flag, a.fault_word, 0x22);
             mbar_wait(&bars.p_full[b], (j / Cfg::kSBuffers) & 1, &abort_flag, a.fault_word, 0x23);
             tc_fence_after();
-            if (lane == 0) FWD_TRACE(0, j, 2);
             if (elect_one()) {
                 // V tile: rows = key index (the MMA's K), 64-column atoms along the head dim (its N)
                 const uint64_t v_desc = make_smem_desc_sw128(smem_u32(sV + vs * Cfg::kTileBytes), kAtomBytes, 1024);
@@ -206,7 +187,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
                 tc_commit(&bars.o_done);
             }
             __syncwarp();
-            if (lane == 0) FWD_TRACE(0, j, 3);
         }
     } else {
         // ------------------------------------------------------------ softmax + correction + epilogue
@@ -226,15 +206,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
         for (int j = 0; j < n_kv; ++j) {
             const int sb = j % Cfg::kSBuffers;
             const uint32_t s_col = Cfg::kColS + sb * 128 + c_begin;
-            if (tid == 0) FWD_TRACE(1, j, 0);
             mbar_wait(&bars.s_full[sb], (j / Cfg::kSBuffers) & 1, &abort_flag, a.fault_word, 0x30);
             tc_fence_after();
-            if (tid == 0) FWD_TRACE(1, j, 1);
             uint32_t sv[kHalfCols];
 #pragma unroll
             for (int c = 0; c < kHalfCols; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, s_col + c), &sv[c]);
             tmem_wait_ld();
-            if (tid == 0) FWD_TRACE(1, j, 2);
             if (j == qt) {  // diagonal tile: key c is visible to query r iff c <= r
 #pragma unroll
                 for (int c = 0; c < kHalfCols; ++c)
@@ -252,7 +229,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             s_xchg[j & 1][half][r] = mx;
             named_bar_sync(1, kSoftmaxThreads);
             mx = fmaxf(mx, s_xchg[j & 1][half ^ 1][r]);
-            if (tid == 0) FWD_TRACE(1, j, 3);
             m_true = fmaxf(m_true, mx * scale_log2);
             const bool move = (j == 0) || (m_true - m_ref > kRescaleThreshold);
             float alpha = 1.0f;
@@ -270,7 +246,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            if (tid == 0) FWD_TRACE(1, j, 4);
             // each half packs its P into the first 32 columns of its OWN 64 score columns
             tmem_st32(tmem_addr(tmem, lane_base, s_col), pk);
             if (j > 0 && __any_sync(0xffffffffu, move)) {
@@ -291,7 +266,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_tc_kernel(const __grid_c
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars.p_full[sb]);
-            if (tid == 0) FWD_TRACE(1, j, 5);
         }
         // ---- epilogue: O / l
         // the two halves of a row add up their sums (buffer parity n_kv & 1 was last used two tiles ago)

@@ -37,37 +37,6 @@
 #include "kernels.cuh"
 #include "tc_common.cuh"
 
-#ifdef B200ATTN_TRACE
-// Debug builds only. Per-CTA life line: {globaltimer at start, first scores ready, loop end, exit, smid, key tiles};
-// and clock64 stamps of CTA 0's softmax thread 0 per tile: {s_full seen, loaded, exps done, arrive}.
-__device__ long long g_fwds_cta_trace[8 * 4096];
-__device__ long long g_fwds_tile_trace[8 * 64];
-extern "C" int b200attn_debug_read_fwds_trace(long long* cta, long long* tile) {
-    cudaError_t e = cudaMemcpyFromSymbol(cta, g_fwds_cta_trace, sizeof(g_fwds_cta_trace));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(tile, g_fwds_tile_trace, sizeof(g_fwds_tile_trace));
-    return (int)e;
-}
-__device__ __forceinline__ long long fwds_globaltimer() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define FWDS_CTA_TRACE(slot, value)                                                  \
-    do {                                                                             \
-        if (blockIdx.x < 4096) g_fwds_cta_trace[blockIdx.x * 8 + (slot)] = (value);  \
-    } while (0)
-#define FWDS_TILE_TRACE(j, point)                                                                    \
-    do {                                                                                             \
-        if (blockIdx.x == 0 && threadIdx.x == 0 && (j) < 64) g_fwds_tile_trace[(j) * 8 + (point)] = clock64(); \
-    } while (0)
-#else
-#define FWDS_CTA_TRACE(slot, value) \
-    do {                            \
-    } while (0)
-#define FWDS_TILE_TRACE(j, point) \
-    do {                          \
-    } while (0)
-#endif
 
 namespace b200attn {
 namespace {
@@ -123,15 +92,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
     const int qt = n_q_tiles - 1 - (a.tile_major_order ? int(blockIdx.x / a.BH) : int(blockIdx.x % n_q_tiles));
     const int hh = bh % a.H, bb = bh / a.H;  // head and batch coordinates of the 4-D tensor maps
     const int n_kv = qt + 1;                                  // key tiles 0..qt; qt is the diagonal tile
-#ifdef B200ATTN_TRACE
-    if (tid == 0) {
-        unsigned int smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        FWDS_CTA_TRACE(0, fwds_globaltimer());
-        FWDS_CTA_TRACE(4, (long long)smid);
-        FWDS_CTA_TRACE(5, (long long)n_kv);
-    }
-#endif
 
     if (tid == 0) {
         mbar_init(&bars.q_full, 1);
@@ -253,10 +213,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
             // D = 128: s_full(j) also means P.V of tile j-1 has retired (MMAs run in order), so O is up to date
             mbar_wait(&bars.s_full, j & 1, &abort_flag, a.fault_word, 0x30);
             tc_fence_after();
-#ifdef B200ATTN_TRACE
-            if (tid == 0 && j == 0) FWDS_CTA_TRACE(1, fwds_globaltimer());
-#endif
-            FWDS_TILE_TRACE(j, 0);
             uint32_t sv[kBN];
 #pragma unroll
             for (int c = 0; c < kBN; c += 32) tmem_ld32(tmem_addr(tmem, lane_base, s_col + c), &sv[c]);
@@ -265,7 +221,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
                 tc_fence_before();
                 mbar_arrive(&bars.s_free);
             }
-            FWDS_TILE_TRACE(j, 1);
             if (j == qt) {  // diagonal tile: key c is visible to query r iff c <= r
 #pragma unroll
                 for (int c = 0; c < kBN; ++c)
@@ -296,7 +251,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
                 pk[c >> 1] = pack_bf16x2(p0, p1);
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            FWDS_TILE_TRACE(j, 2);
             if (Cfg::kSeparateP && j > 0) {  // P_{j-1} V_{j-1} must have read the P columns (and updated O)
                 mbar_wait(&bars.o_done, (j - 1) & 1, &abort_flag, a.fault_word, 0x31);
                 tc_fence_after();
@@ -318,15 +272,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars.p_full);
-            FWDS_TILE_TRACE(j, 3);
         }
-#ifdef B200ATTN_TRACE
-        if (tid == 0) FWDS_CTA_TRACE(2, fwds_globaltimer());
-#endif
         // ---- epilogue: O / l
         mbar_wait(&bars.o_done, (n_kv - 1) & 1, &abort_flag, a.fault_word, 0x32);
         tc_fence_after();
-        FWDS_TILE_TRACE(n_kv, 0);
         const float inv_l = 1.0f / l_run;
         const int row_g = qt * kBM + r;
         const long long stat_idx = (long long)bh * a.T + row_g;
@@ -377,9 +326,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_tc_short_kernel(const __
     tc_fence_before();
     __syncthreads();
     if (warp == 4) tmem_dealloc(tmem, Cfg::kTmemCols);
-#ifdef B200ATTN_TRACE
-    if (tid == 0) FWDS_CTA_TRACE(3, fwds_globaltimer());
-#endif
 }
 
 template <int D, bool OUT_F32>
