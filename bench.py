@@ -189,6 +189,7 @@ def run_gpt_step(args):
     steps = max(1, min(args.steps, 20))
     env = dict(os.environ)
     env.setdefault("B200ATTN_MATH", "bf16")  # attention through the tcgen05 kernels (the reference arm ignores it)
+    env.setdefault("B200ATTN_FUSED_CONVERT", "1")  # BF16 copies of q, k, v, dO come out of the layout launchers
     if args.gemm != "reference":
         env["B200GEMM_MATH"] = args.gemm
     res = subprocess.run([exe, "--steps", str(steps), "--warmup", str(min(args.warmup, 3))], env=env, capture_output=True, text=True)

@@ -42,6 +42,19 @@ const char* b200attn_last_error(void);
  * variable B200ATTN_MATH ("fp32" or "bf16"), else FP32. */
 int b200attn_set_math_mode(int mode);
 int b200attn_get_math_mode(void);
+/* Fused conversion for the float* API in BF16 math mode (off by default; initial value: the environment variable
+ * B200ATTN_FUSED_CONVERT). When on, b200attn_qkv_split_f32 and b200attn_split_heads_f32 also write BF16 copies of
+ * their FP32 outputs in the same pass (library-owned, keyed by the output tensor's address), and a later
+ * b200attn_fwd_f32 / b200attn_bwd_f32 whose q, k, v (dO) are those very tensors uses the copies instead of running
+ * one conversion pass per operand - seven passes per layer of src/model.cu:305-336,602-653. The caller promises not
+ * to modify such a tensor between the layout call and the attention calls that consume it (the reference model does
+ * not); a tensor that did not come from one of the two launchers is converted as before. The copies (2 bytes per
+ * element of every registered tensor) are allocated on first use outside stream capture and freed by
+ * b200attn_release. b200attn_fused_convert_hits counts the operand conversions skipped so far. No reference
+ * counterpart (the reference is FP32 throughout). */
+int b200attn_set_fused_convert(int on);
+int b200attn_get_fused_convert(void);
+long long b200attn_fused_convert_hits(void);
 /* Grow the library-owned scratch of the current device so that later calls with shapes up to
  * (B*H, T, d) allocate nothing - required before such calls are recorded in a CUDA graph. */
 int b200attn_reserve(int BH, int T, int d);

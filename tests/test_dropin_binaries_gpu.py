@@ -56,13 +56,15 @@ def test_reference_model_meets_its_parity_gate(tmp_path, case, tiled):
     assert _max_abs(load("cuda_grads.bin"), load("pytorch_grads.bin")) <= 5e-5
 
 
-def test_reference_model_through_the_tensor_cores(tmp_path):
-    """Same model binary, d_head = 64, attention routed to the tcgen05 kernels by B200ATTN_MATH=bf16.
+@pytest.mark.parametrize("fused", ["0", "1"])
+def test_reference_model_through_the_tensor_cores(tmp_path, fused):
+    """Same model binary, d_head = 64, attention routed to the tcgen05 kernels by B200ATTN_MATH=bf16 - with one
+    conversion pass per operand, and with the BF16 copies written by the layout launchers (B200ATTN_FUSED_CONVERT=1).
     BF16 operands cannot meet the FP32 gate; the whole-model error stays within the BF16 gates."""
     exe = _binary("parity_audit")
     work = tmp_path / "bf16"
     shutil.copytree(os.path.join(GOLDEN_DIR, "parity_audit_d64"), work)
-    env = dict(os.environ, B200ATTN_MATH="bf16")
+    env = dict(os.environ, B200ATTN_MATH="bf16", B200ATTN_FUSED_CONVERT=fused)
     res = subprocess.run([exe, str(work), "--tiled_attn"], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "[b200attn]" not in res.stderr

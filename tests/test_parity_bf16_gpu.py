@@ -227,3 +227,45 @@ def test_module_bf16_mode_matches_fp32_mode(pkg):
     for a, b in zip(res[0], res[1]):
         m = orc.compute_metrics(host(b), host(a))
         assert m["rel_l2"] <= 2e-2, m
+
+
+def test_fused_conversion_in_the_layout_launchers(pkg, ops):
+    """FP32 launch API in BF16 math mode with b200attn_set_fused_convert(1): the split / head-split launchers leave
+    BF16 copies of q, k, v and dO, the attention launchers pick them up (7 operand conversions skipped per layer pass)
+    and every result is bit-identical to the path that converts operand by operand; dK, dV and O exactly, dQ up to the
+    order of its floating-point reductions. A tensor that did not come from a layout launcher is converted as before."""
+    B, T, H, d = 2, 192, 3, 64
+    C, scale = H * d, 1.0 / math.sqrt(d)
+    qkv = ops.fill_normal_(torch.empty(B, T, 3 * C, device="cuda"), seed=61)
+    dmerged = ops.fill_normal_(torch.empty(B, T, C, device="cuda"), seed=62)
+
+    def run(fused):
+        ops.set_fused_convert(fused)
+        q, k, v, out, dO, dq, dk, dv = (torch.empty(B, H, T, d, device="cuda") for _ in range(8))
+        m, l, ws = (torch.empty(B, H, T, device="cuda") for _ in range(3))
+        ops.qkv_split_transpose_forward(qkv, q, k, v, B, T, H, d)
+        ops.tiled_causal_attention_forward(q, k, v, out, B, H, T, d, scale, m, l)
+        ops.head_merge_transpose_backward(dmerged, dO, B, H, T, d)
+        ops.tiled_causal_attention_backward(q, k, v, out, dO, m, l, dq, dk, dv, ws, B, H, T, d, scale)
+        ops.check_device_fault()
+        return q, k, v, out, dO, dq, dk, dv
+
+    ops.set_math_mode("bf16")
+    try:
+        plain = run(False)
+        hits0 = ops.fused_convert_hits()
+        fused = run(True)
+        assert ops.fused_convert_hits() - hits0 == 7  # q, k, v (forward) + q, k, v, dO (backward)
+        # tensors the layout launchers never saw: converted as before, no new hits
+        other = [t.clone() for t in plain[:3]]
+        out2, m2, l2 = torch.empty_like(other[0]), torch.empty(B, H, T, device="cuda"), torch.empty(B, H, T, device="cuda")
+        ops.tiled_causal_attention_forward(other[0], other[1], other[2], out2, B, H, T, d, scale, m2, l2)
+        assert ops.fused_convert_hits() - hits0 == 7 and torch.equal(out2, plain[3])
+    finally:
+        ops.set_fused_convert(False)
+        ops.set_math_mode("fp32")
+    for i, name in enumerate(("q", "k", "v", "out", "dO")):
+        assert torch.equal(plain[i], fused[i]), name
+    assert torch.equal(plain[6], fused[6]) and torch.equal(plain[7], fused[7])  # dK, dV
+    diff = (plain[5] - fused[5]).abs().max().item()
+    assert diff <= 2.0 ** -6 * max(1.0, plain[5].abs().max().item())

@@ -42,6 +42,12 @@ int initial_math_mode() {
     return B200ATTN_MATH_FP32;
 }
 std::atomic<int> g_math_mode{initial_math_mode()};
+int initial_fused_convert() {
+    const char* s = getenv("B200ATTN_FUSED_CONVERT");
+    return (s && s[0] != '\0' && s[0] != '0') ? 1 : 0;
+}
+std::atomic<int> g_fused_convert{initial_fused_convert()};
+std::atomic<long long> g_shadow_hits{0};
 
 // ------------------------------------------------------------------ per-device state
 constexpr int kMaxDevices = 64;
@@ -52,6 +58,14 @@ struct DeviceState {
     unsigned int* work_counter = nullptr;  // word 4 of the same block: item counter of the persistent backward
     uint8_t* scratch = nullptr;
     size_t scratch_bytes = 0;
+    // BF16 copies of FP32 tensors, written by the layout launchers and consumed by the attention launchers of the
+    // FP32 API in BF16 math mode (b200attn_set_fused_convert): keyed by the FP32 tensor's address.
+    struct Shadow {
+        const void* key;
+        size_t n;  // elements
+        __nv_bfloat16* data;
+    };
+    std::vector<Shadow> shadows;
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mutex;
@@ -127,6 +141,37 @@ int device_state(cudaStream_t stream, DeviceState** out) {
 }
 
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// The BF16 copy registered for the FP32 tensor at `key` with exactly n elements, or NULL.
+__nv_bfloat16* find_shadow(DeviceState* st, const void* key, size_t n) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (auto& sh : st->shadows)
+        if (sh.key == key && sh.n == n) return sh.data;
+    return nullptr;
+}
+// The same, created on first use (never while `stream` is capturing: NULL then, and the caller falls back).
+__nv_bfloat16* find_or_make_shadow(DeviceState* st, const void* key, size_t n, cudaStream_t stream) {
+    if (__nv_bfloat16* p = find_shadow(st, key, n)) return p;
+    if (stream_is_capturing(stream)) return nullptr;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (auto it = st->shadows.begin(); it != st->shadows.end();) {  // a tensor of another size now lives at this address
+        if (it->key == key) {
+            cudaDeviceSynchronize();
+            cudaFree(it->data);
+            it = st->shadows.erase(it);
+        } else {
+            ++it;
+        }
+    }
+    __nv_bfloat16* p = nullptr;
+    if (cudaMalloc(&p, round_up(n * sizeof(__nv_bfloat16), 256)) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    st->shadows.push_back(DeviceState::Shadow{key, n, p});
+    return p;
+}
+bool fused_convert_on() { return g_fused_convert.load() != 0 && g_math_mode.load() == B200ATTN_MATH_BF16; }
 
 // Makes the scratch of this device at least `bytes` large. Growing synchronises the device and
 // is refused while `stream` is capturing.
@@ -336,8 +381,17 @@ extern "C" int b200attn_release(void) {
     if (st.scratch) cudaFree(st.scratch);
     st.scratch = nullptr;
     st.scratch_bytes = 0;
+    for (auto& sh : st.shadows) cudaFree(sh.data);
+    st.shadows.clear();
     return B200ATTN_OK;
 }
+
+extern "C" int b200attn_set_fused_convert(int on) {
+    g_fused_convert.store(on ? 1 : 0);
+    return B200ATTN_OK;
+}
+extern "C" int b200attn_get_fused_convert(void) { return g_fused_convert.load(); }
+extern "C" long long b200attn_fused_convert_hits(void) { return g_shadow_hits.load(); }
 
 extern "C" int b200attn_check_device_fault(unsigned int* code) {
     // Two words can hold a fault: the heap word of the allocating entry points (it exists only once one of
@@ -413,6 +467,19 @@ extern "C" int b200attn_qkv_split_f32(const float* qkv, float* q, float* k, floa
     if (rc) return rc;
     if ((long long)B * T * H == 0) return B200ATTN_OK;
     REQUIRE_PTR(fn, qkv); REQUIRE_PTR(fn, q); REQUIRE_PTR(fn, k); REQUIRE_PTR(fn, v);
+    if (fused_convert_on() && dual_layout_supported(d, qkv, q, k, v)) {
+        // BF16 copies of q, k, v in the same pass, for the attention launchers that follow (no conversion passes there)
+        DeviceState* st = nullptr;
+        if ((rc = device_state((cudaStream_t)stream, &st))) return rc;
+        const size_t n = size_t(B) * T * H * d;
+        __nv_bfloat16* qb = find_or_make_shadow(st, q, n, (cudaStream_t)stream);
+        __nv_bfloat16* kb = find_or_make_shadow(st, k, n, (cudaStream_t)stream);
+        __nv_bfloat16* vb = find_or_make_shadow(st, v, n, (cudaStream_t)stream);
+        if (qb && kb && vb) {
+            RETURN_IF_CUDA(launch_qkv_split_dual(qkv, q, k, v, qb, kb, vb, B, T, H, d, (cudaStream_t)stream), fn);
+            return B200ATTN_OK;
+        }
+    }
     RETURN_IF_CUDA(launch_qkv_split<float>(qkv, q, k, v, B, T, H, d, (cudaStream_t)stream), fn);
     return B200ATTN_OK;
 }
@@ -474,12 +541,18 @@ extern "C" int b200attn_fwd_f32(const float* q, const float* k, const float* v, 
     const size_t n = size_t(BH) * T * d;
     if ((rc = ensure_scratch(st, scratch_for(BH, T, d), stream))) return rc;
     Bump bump{st->scratch};
-    __nv_bfloat16* qb = bump.take<__nv_bfloat16>(n);
-    __nv_bfloat16* kb = bump.take<__nv_bfloat16>(n);
-    __nv_bfloat16* vb = bump.take<__nv_bfloat16>(n);
-    RETURN_IF_CUDA(launch_f32_to_bf16(q, qb, (long long)n, stream), "convert q");
-    RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
-    RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
+    const __nv_bfloat16* qb = fused_convert_on() ? find_shadow(st, q, n) : nullptr;
+    const __nv_bfloat16* kb = fused_convert_on() ? find_shadow(st, k, n) : nullptr;
+    const __nv_bfloat16* vb = fused_convert_on() ? find_shadow(st, v, n) : nullptr;
+    if (qb && kb && vb) {
+        g_shadow_hits.fetch_add(3);  // the split launcher left BF16 copies of these very tensors
+    } else {
+        __nv_bfloat16 *q2 = bump.take<__nv_bfloat16>(n), *k2 = bump.take<__nv_bfloat16>(n), *v2 = bump.take<__nv_bfloat16>(n);
+        RETURN_IF_CUDA(launch_f32_to_bf16(q, q2, (long long)n, stream), "convert q");
+        RETURN_IF_CUDA(launch_f32_to_bf16(k, k2, (long long)n, stream), "convert k");
+        RETURN_IF_CUDA(launch_f32_to_bf16(v, v2, (long long)n, stream), "convert v");
+        qb = q2, kb = k2, vb = v2;
+    }
     const Layout sl = slab_layout(BH, T, d);
     return run_fwd_tc(st, qb, kb, vb, out, true, m_out, l_out, nullptr, 1, BH, T, d, sl, sl, scale, stream);
 }
@@ -536,17 +609,32 @@ extern "C" int b200attn_bwd_f32(const float* q, const float* k, const float* v, 
     const size_t n = size_t(BH) * T * d;
     if ((rc = ensure_scratch(st, scratch_for(BH, T, d), stream))) return rc;
     Bump bump{st->scratch};
-    __nv_bfloat16* qb = bump.take<__nv_bfloat16>(n);
-    __nv_bfloat16* kb = bump.take<__nv_bfloat16>(n);
-    __nv_bfloat16* vb = bump.take<__nv_bfloat16>(n);
-    __nv_bfloat16* dob = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* q2 = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* k2 = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* v2 = bump.take<__nv_bfloat16>(n);
+    __nv_bfloat16* do2 = bump.take<__nv_bfloat16>(n);
     float* lse2 = bump.take<float>(size_t(rows));
+    const bool fused = fused_convert_on();
+    const __nv_bfloat16* qb = fused ? find_shadow(st, q, n) : nullptr;
+    const __nv_bfloat16* kb = fused ? find_shadow(st, k, n) : nullptr;
+    const __nv_bfloat16* vb = fused ? find_shadow(st, v, n) : nullptr;
+    const __nv_bfloat16* dob = fused ? find_shadow(st, dO, n) : nullptr;
     BwdStatRows ext{nullptr, nullptr, 0.f};
     if (use_persistent_bwd(d, scale)) ext = BwdStatRows{bump.take<__nv_bfloat16>(size_t(rows) * 16), bump.take<__nv_bfloat16>(size_t(rows) * 16), 1.0f / scale};
-    RETURN_IF_CUDA(launch_f32_to_bf16(q, qb, (long long)n, stream), "convert q");
-    RETURN_IF_CUDA(launch_f32_to_bf16(k, kb, (long long)n, stream), "convert k");
-    RETURN_IF_CUDA(launch_f32_to_bf16(v, vb, (long long)n, stream), "convert v");
-    RETURN_IF_CUDA(launch_f32_to_bf16(dO, dob, (long long)n, stream), "convert dO");
+    if (qb && kb && vb) {
+        g_shadow_hits.fetch_add(3);
+    } else {
+        RETURN_IF_CUDA(launch_f32_to_bf16(q, q2, (long long)n, stream), "convert q");
+        RETURN_IF_CUDA(launch_f32_to_bf16(k, k2, (long long)n, stream), "convert k");
+        RETURN_IF_CUDA(launch_f32_to_bf16(v, v2, (long long)n, stream), "convert v");
+        qb = q2, kb = k2, vb = v2;
+    }
+    if (dob) {
+        g_shadow_hits.fetch_add(1);
+    } else {
+        RETURN_IF_CUDA(launch_f32_to_bf16(dO, do2, (long long)n, stream), "convert dO");
+        dob = do2;
+    }
     // dq is the FP32 accumulator itself: partial sums are reduced straight into the caller's buffer,
     // which the pre-pass clears
     RETURN_IF_CUDA(launch_bwd_prepass<float>(o, dO, m, l, nullptr, workspace, lse2, dq, rows, d, stream, st->work_counter, ext), "pre-pass");
@@ -572,6 +660,14 @@ extern "C" int b200attn_split_heads_f32(const float* dout, float* din, int B, in
     if (rc) return rc;
     if ((long long)B * T * H == 0) return B200ATTN_OK;
     REQUIRE_PTR(fn, dout); REQUIRE_PTR(fn, din);
+    if (fused_convert_on() && dual_layout_supported(d, dout, din, din, din)) {
+        DeviceState* st = nullptr;
+        if ((rc = device_state((cudaStream_t)stream, &st))) return rc;
+        if (__nv_bfloat16* db = find_or_make_shadow(st, din, size_t(B) * H * T * d, (cudaStream_t)stream)) {
+            RETURN_IF_CUDA(launch_split_heads_dual(dout, din, db, B, H, T, d, (cudaStream_t)stream), fn);
+            return B200ATTN_OK;
+        }
+    }
     RETURN_IF_CUDA(launch_split_heads<float>(dout, din, B, H, T, d, (cudaStream_t)stream), fn);
     return B200ATTN_OK;
 }

@@ -41,6 +41,12 @@ template <typename TIn>
 cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream);
 template <typename TOut>
 cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T, int d, cudaStream_t stream);
+// FP32 outputs plus BF16 copies in the same pass (d % 8 == 0, 16-byte aligned tensors: dual_layout_supported).
+bool dual_layout_supported(int d, const void* a, const void* b, const void* c, const void* e);
+cudaError_t launch_qkv_split_dual(const float* qkv, float* q, float* k, float* v, __nv_bfloat16* qb, __nv_bfloat16* kb,
+                                  __nv_bfloat16* vb, int B, int T, int H, int d, cudaStream_t stream);
+cudaError_t launch_split_heads_dual(const float* dout, float* din, __nv_bfloat16* din_bf16, int B, int H, int T, int d,
+                                    cudaStream_t stream);
 // dst = bf16(src * scale), elementwise
 cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream, float scale = 1.0f);
 cudaError_t launch_fill_normal_f32(float* dst, long long n, unsigned long long seed, long long offset,

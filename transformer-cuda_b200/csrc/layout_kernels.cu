@@ -115,6 +115,56 @@ __global__ void __launch_bounds__(kThreads) qkv_split_kernel(const float* __rest
     store_from_f32<VEC>(v + dst, a);
 }
 
+// The FP32 split with BF16 copies of q, k, v written in the same pass (8 elements per thread and tensor): what the
+// FP32 launch API in BF16 math mode would otherwise produce with three separate conversion passes.
+__global__ void __launch_bounds__(kThreads) qkv_split_dual_kernel(const float* __restrict__ qkv, float* __restrict__ q,
+                                                                 float* __restrict__ k, float* __restrict__ v,
+                                                                 __nv_bfloat16* __restrict__ qb, __nv_bfloat16* __restrict__ kb,
+                                                                 __nv_bfloat16* __restrict__ vb, int T, int H, int d,
+                                                                 long long groups) {
+    long long g = blockIdx.x * (long long)kThreads + threadIdx.x;
+    if (g >= groups) return;
+    const int dv = d / 8;
+    int e = int(g % dv) * 8;
+    long long r = g / dv;
+    int h = int(r % H);
+    r /= H;
+    int t = int(r % T);
+    long long b = r / T;
+    const long long C = (long long)H * d;
+    const float* src = qkv + (b * T + t) * 3 * C + (long long)h * d + e;
+    long long dst = ((b * H + h) * T + t) * d + e;
+    float a[8];
+    load_as_f32<8>(src, a);
+    store_from_f32<8>(q + dst, a);
+    store_from_f32<8>(qb + dst, a);
+    load_as_f32<8>(src + C, a);
+    store_from_f32<8>(k + dst, a);
+    store_from_f32<8>(kb + dst, a);
+    load_as_f32<8>(src + 2 * C, a);
+    store_from_f32<8>(v + dst, a);
+    store_from_f32<8>(vb + dst, a);
+}
+// (B,T,H*d) FP32 -> (B,H,T,d) FP32 and BF16 in one pass.
+__global__ void __launch_bounds__(kThreads) split_heads_dual_kernel(const float* __restrict__ merged_in, float* __restrict__ head_out,
+                                                                   __nv_bfloat16* __restrict__ head_out_bf16, int T, int H, int d,
+                                                                   long long groups) {
+    long long g = blockIdx.x * (long long)kThreads + threadIdx.x;
+    if (g >= groups) return;
+    const int dv = d / 8;
+    int e = int(g % dv) * 8;
+    long long r = g / dv;
+    int h = int(r % H);
+    r /= H;
+    int t = int(r % T);
+    long long b = r / T;
+    float a[8];
+    load_as_f32<8>(merged_in + ((b * T + t) * H + h) * d + e, a);
+    const long long head = ((b * H + h) * T + t) * d + e;
+    store_from_f32<8>(head_out + head, a);
+    store_from_f32<8>(head_out_bf16 + head, a);
+}
+
 template <typename TIn, int VEC>
 __global__ void __launch_bounds__(kThreads) qkv_merge_grad_kernel(const TIn* __restrict__ dq, const TIn* __restrict__ dk,
                                                                  const TIn* __restrict__ dv, float* __restrict__ dqkv,
@@ -292,6 +342,26 @@ cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T
 }
 template cudaError_t launch_split_heads<float>(const float*, float*, int, int, int, int, cudaStream_t);
 template cudaError_t launch_split_heads<__nv_bfloat16>(const float*, __nv_bfloat16*, int, int, int, int, cudaStream_t);
+
+bool dual_layout_supported(int d, const void* a, const void* b, const void* c, const void* e) {
+    return d % 8 == 0 && aligned16(a) && aligned16(b) && aligned16(c) && aligned16(e);
+}
+cudaError_t launch_qkv_split_dual(const float* qkv, float* q, float* k, float* v, __nv_bfloat16* qb, __nv_bfloat16* kb,
+                                  __nv_bfloat16* vb, int B, int T, int H, int d, cudaStream_t stream) {
+    const long long n = (long long)B * T * H * d;
+    if (n == 0) return cudaSuccess;
+    const long long groups = n / 8;
+    qkv_split_dual_kernel<<<blocks_for(groups), kThreads, 0, stream>>>(qkv, q, k, v, qb, kb, vb, T, H, d, groups);
+    return cudaGetLastError();
+}
+cudaError_t launch_split_heads_dual(const float* dout, float* din, __nv_bfloat16* din_bf16, int B, int H, int T, int d,
+                                    cudaStream_t stream) {
+    const long long n = (long long)B * T * H * d;
+    if (n == 0) return cudaSuccess;
+    const long long groups = n / 8;
+    split_heads_dual_kernel<<<blocks_for(groups), kThreads, 0, stream>>>(dout, din, din_bf16, T, H, d, groups);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_f32_to_bf16(const float* src, __nv_bfloat16* dst, long long n, cudaStream_t stream, float scale) {
     if (n == 0) return cudaSuccess;

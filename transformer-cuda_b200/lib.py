@@ -29,6 +29,9 @@ _SIGNATURES = {
     "b200attn_last_error": ([], ctypes.c_char_p),
     "b200attn_set_math_mode": ([_I], _I),
     "b200attn_get_math_mode": ([], _I),
+    "b200attn_set_fused_convert": ([_I], _I),
+    "b200attn_get_fused_convert": ([], _I),
+    "b200attn_fused_convert_hits": ([], _LL),
     "b200attn_reserve": ([_I, _I, _I], _I),
     "b200attn_release": ([], _I),
     "b200attn_check_device_fault": ([ctypes.POINTER(ctypes.c_uint)], _I),

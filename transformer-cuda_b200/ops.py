@@ -233,6 +233,16 @@ def get_math_mode():
     return "bf16" if _lib.load().b200attn_get_math_mode() == _lib.MATH_BF16 else "fp32"
 
 
+def set_fused_convert(on):
+    """BF16 copies of q, k, v / dO written by the FP32 layout launchers and reused by the FP32 attention launchers in
+    BF16 math mode (see include/b200attn.h)."""
+    _lib.call("b200attn_set_fused_convert", 1 if on else 0)
+
+
+def fused_convert_hits():
+    return int(_lib.load().b200attn_fused_convert_hits())
+
+
 def reserve(BH, T, d):
     _lib.call("b200attn_reserve", int(BH), int(T), int(d))
 
