@@ -80,3 +80,28 @@ def test_python_launchers_reject_cpu_tensors(pkg):
     x = torch.zeros(1, 1, 8, 32)
     with pytest.raises(pkg.lib.B200AttnError):
         pkg.ops.tiled_causal_attention_forward(x, x, x, x, 1, 1, 8, 32, 1.0)
+
+
+def test_loss_library_exports_its_header(pkg):
+    """libb200loss.so: every symbol of include/b200loss.h is exported and bound, the C++ launcher with the
+    reference's signature (include/kernels/loss.cuh:8-15) is present, and bad arguments fail before any CUDA call."""
+    import importlib
+    import __graft_entry__ as entry
+    loss_ops = importlib.import_module(pkg.__name__ + ".loss_ops")
+    if not os.path.exists(loss_ops.SO_PATH):
+        entry.build()
+    so = loss_ops.load()
+    names = loss_ops.declared_symbols()
+    assert sorted(loss_ops._SIGNATURES) == names
+    for n in names:
+        assert hasattr(so, n), n
+    out = subprocess.run(["nm", "-D", "--defined-only", "-C", loss_ops.SO_PATH], capture_output=True, text=True, check=True).stdout
+    assert re.search(r"\bcross_entropy_forward_backward\(float const\*, int const\*, float\*, float\*, int, int, int, CUstream_st\*\)", out)
+    assert re.search(r"\bcross_entropy_forward_backward_device\(", out)
+    with open(os.path.join(ROOT, "include", "kernels", "loss.cuh")) as f:
+        text = re.sub(r"\s+", " ", f.read())
+    assert ("void cross_entropy_forward_backward(const float* logits, const int* targets, float* dlogits, float* host_loss, "
+            "int B, int T, int V, cudaStream_t stream = 0);") in text
+    assert so.b200loss_cross_entropy(None, None, None, None, 1, 1, 8, None) == -1
+    assert b"NULL" in so.b200loss_last_error()
+    assert so.b200loss_max_resident_vocab() >= 50257

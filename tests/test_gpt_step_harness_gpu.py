@@ -41,7 +41,7 @@ def _run(exe, env_extra, world=1):
     outs = [p.communicate(timeout=300) for p in procs]
     for p, (out, err) in zip(procs, outs):
         assert p.returncode == 0, out + err
-        assert "[b200attn]" not in err
+        assert "[b200attn]" not in err and "[b200loss]" not in err and "[b200opt]" not in err
     line = [l for l in outs[0][0].splitlines() if l.startswith("{")][-1]
     return json.loads(line)
 
@@ -53,6 +53,16 @@ def test_one_rank_bf16_attention_matches_fp32_parity_mode():
     assert "BF16" in got["attention"] and "FP32" in ref["attention"]
     assert ref["n_gpus"] == 1 and ref["allreduce_ms_per_step"] == 0.0
     assert abs(got["loss"] - ref["loss"]) <= 2e-2 * max(1.0, abs(ref["loss"])), (got["loss"], ref["loss"])
+
+
+def test_every_dropin_together_follows_the_same_loss_curve():
+    """build/gpt_step_dp_b200_all (attention, GEMM, loss and AdamW drop-ins) against build/gpt_step_dp_b200_gemm (the
+    reference's loss.cu and optimizer.cu) in FP32 arithmetic: same tokens, same initial weights, three optimizer steps;
+    the loss after the third step depends on both updates before it and on the loss kernel itself."""
+    env = {"B200ATTN_MATH": "fp32", "B200GEMM_MATH": "fp32"}
+    ref = _run(_binary("gpt_step_dp_b200_gemm"), env)
+    got = _run(_binary("gpt_step_dp_b200_all"), env)
+    assert abs(got["loss"] - ref["loss"]) <= 1e-4 * max(1.0, abs(ref["loss"])), (got["loss"], ref["loss"])
 
 
 def test_two_ranks_average_their_gradients():

@@ -126,3 +126,24 @@ def test_gpt_port_matches_the_reference_generator(case):
     assert np.abs(logits.detach().numpy().ravel() - load("pytorch_logits.bin")).max() <= 1e-5
     assert abs(float(loss) - float(load("pytorch_loss.bin")[0])) <= 1e-5
     assert np.abs(flat.grad.numpy() - load("pytorch_grads.bin")).max() <= 5e-5
+
+
+@pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])
+def test_cross_entropy_oracle_matches_the_reference_generator(case):
+    """oracle/cross_entropy_oracle.py against the reference generator's own files: its loss from its logits and
+    targets (1e-5, the gate of scripts/compare_parity.py:108-117), and d_logits against autograd of
+    F.cross_entropy, the loss of pytorch_src/model.py:118-121."""
+    import torch
+    from oracle import cross_entropy_oracle as ce
+    d = os.path.join(GOLDEN_DIR, case)
+    B, T, C, L, H, V = (int(x) for x in open(os.path.join(d, "config.txt")).read().split())
+    logits = np.fromfile(os.path.join(d, "pytorch_logits.bin"), dtype=np.float32).reshape(B * T, V)
+    targets = np.fromfile(os.path.join(d, "targets.bin"), dtype=np.int32)
+    dlogits, loss = ce.cross_entropy_forward_backward(logits, targets)
+    assert abs(loss - float(np.fromfile(os.path.join(d, "pytorch_loss.bin"), dtype=np.float32)[0])) <= 1e-5
+    lt = torch.from_numpy(logits.astype(np.float64)).requires_grad_(True)
+    torch.nn.functional.cross_entropy(lt, torch.from_numpy(targets.astype(np.int64))).backward()
+    assert np.abs(dlogits - lt.grad.numpy()).max() <= 1e-9
+    # float32 arithmetic, as the reference kernel runs it, stays within the same gate
+    d32, loss32 = ce.cross_entropy_forward_backward(logits, targets, dtype=np.float32)
+    assert abs(loss32 - loss) <= 1e-5 and np.abs(d32 - dlogits).max() <= 1e-7

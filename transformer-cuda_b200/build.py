@@ -1,6 +1,7 @@
 """Builds the engine in-tree with nvcc for sm_100a: lib/libb200attn.so (C ABI + the C++ launch API)
 and lib/libb200attn.a (the same objects, for static linking in place of the reference's
-src/kernels/attention.cu). Rebuilds only when a source is newer than the library."""
+src/kernels/attention.cu); beside them the drop-ins for the callers of the path: lib/libb200gemm.a
+(src/kernels/matmul.cu) and lib/libb200loss.so / .a (src/kernels/loss.cu). Rebuilds only when a source is newer than the library."""
 import os
 import shutil
 import subprocess
@@ -17,6 +18,8 @@ FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", 
 SO = os.path.join(LIBDIR, "libb200attn.so")
 AR = os.path.join(LIBDIR, "libb200attn.a")
 GEMM_AR = os.path.join(LIBDIR, "libb200gemm.a")
+LOSS_SO = os.path.join(LIBDIR, "libb200loss.so")
+LOSS_AR = os.path.join(LIBDIR, "libb200loss.a")
 
 
 def _nvcc():
@@ -75,6 +78,19 @@ def build(verbose=False, force=False, ptxas_info=False):
         if os.path.exists(GEMM_AR):
             os.remove(GEMM_AR)
         subprocess.check_call(["ar", "rcs", GEMM_AR, gemm_obj])
+    # the loss drop-in (fused softmax cross-entropy): its own shared + static library, no dependency on the attention engine
+    loss_src = os.path.join(HERE, "loss", "cross_entropy.cu")
+    loss_obj = os.path.join(OBJDIR, "cross_entropy.o")
+    loss_deps = [loss_src, os.path.join(CSRC, "tc_common.cuh"), os.path.join(HERE, "..", "include", "kernels", "loss.cuh"),
+                 os.path.join(HERE, "..", "include", "b200loss.h")]
+    if force or _stale(loss_obj, loss_deps):
+        subprocess.check_call([nvcc] + ARCH + FLAGS + ["-I", os.path.join(HERE, "..", "include"), "-I", CSRC, "-c", loss_src, "-o", loss_obj])
+    if force or _stale(LOSS_SO, [loss_obj]):
+        subprocess.check_call([nvcc] + ARCH + ["-shared", "-o", LOSS_SO, loss_obj, "-lcudart"])
+    if force or _stale(LOSS_AR, [loss_obj]):
+        if os.path.exists(LOSS_AR):
+            os.remove(LOSS_AR)
+        subprocess.check_call(["ar", "rcs", LOSS_AR, loss_obj])
     return SO
 
 
