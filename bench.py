@@ -179,7 +179,8 @@ def run_gpt_step(args):
     if args.impl == "reference":
         name = "gpt_step_dp_ref"
     else:
-        name = "gpt_step_dp_b200" if args.gemm == "reference" else "gpt_step_dp_b200_gemm"
+        name = "gpt_step_dp_b200" if args.gemm == "reference" else \
+            ("gpt_step_dp_b200_all" if args.loss_adamw == "dropin" else "gpt_step_dp_b200_gemm")
     exe = os.path.join(ROOT, "build", name)
     if not os.path.exists(exe):
         if rank == 0:
@@ -207,7 +208,9 @@ def run_gpt_step(args):
             "config": {"workload": "c4: GPT training step L=12 C=768 H=12 d_ff=3072 V=50257 T=1024, per-GPU B=16, AdamW, "
                                    "data-parallel NCCL all-reduce of gradients", **child["config"], "attention": child["attention"],
                        "gemm": "reference FP32 cuBLAS wrappers" if (args.impl == "reference" or args.gemm == "reference")
-                               else f"GEMM drop-in, B200GEMM_MATH={args.gemm}"},
+                               else f"GEMM drop-in, B200GEMM_MATH={args.gemm}",
+                       "loss_adamw": "loss and AdamW drop-ins (libb200loss, optim/adamw_dropin.cu)" if name.endswith("_all")
+                                     else "reference loss.cu and optimizer.cu"},
             "loss_after_last_step": child["loss"],
             "allreduce_ms_per_step": child.get("allreduce_ms_per_step"),
             "allreduce": "one in-place ncclAllReduce(avg) of the 163 M-float gradient buffer per step, timed with CUDA events on rank 0"}
@@ -328,6 +331,19 @@ def run_path_kernels(args, B, H, T, d):
 
     ms_packed = timed(packed_step, copies)
     ms_chain = timed(chain_step, copies)
+    del pq, pdo, pout, pdqkv, qkv, q32, k32, v32, qb, kb, vb, merged, scores, probs
+    torch.cuda.empty_cache()
+    # the loss launcher at the head of the model's backward, on the GPT step's shape (3.3 GB in, 3.3 GB out: beyond L2)
+    import importlib
+    loss_ops = importlib.import_module(pkg.__name__ + ".loss_ops")
+    cB, cT, cV = 16, 1024, 50257
+    logits = torch.randn(cB, cT, cV, device=dev)
+    targets = torch.randint(0, cV, (cB * cT,), device=dev, dtype=torch.int32)
+    dlogits = torch.empty_like(logits)
+    iters = 10
+    ms = timed(lambda c: loss_ops.cross_entropy_forward_backward(logits, targets, dlogits=dlogits))
+    loss_ops.check_device_fault()
+    row(f"cross_entropy_forward_backward (rows={cB * cT}, V={cV})", "loss.cu:97", ms, 8 * cB * cT * cV)
     print(json.dumps({
         "suite": "path-kernels", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm"], "peak_source": peaks["source"],
         "config": {"workload": workload_name(args, B, H, T, d), "l2": f"{copies} rotating buffer sets"},
@@ -474,6 +490,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemm", default="bf16", choices=["reference", "fp32", "bf16"],
                     help="c4 only: the model's GEMM wrappers - the reference's own FP32 ones, or the drop-in in FP32 / BF16 arithmetic")
+    ap.add_argument("--loss-adamw", default="dropin", choices=["reference", "dropin"],
+                    help="c4 only, with a GEMM drop-in: the model's loss launcher and optimizer - the reference's, or the drop-ins")
     ap.add_argument("--kernel-event-stride", type=int, default=0,
                     help="bracket every N-th launch of each tensor-core kernel with CUDA events inside the timed region "
                          "(roofline durations); events between kernels undo their back-to-back launch, so N=1 slows the "

@@ -24,7 +24,7 @@ REF_BIN = os.path.join(ROOT, "oracle", "_ref")
 def _binary(name):
     path = os.path.join(REF_BIN, name)
     if not os.path.exists(path):
-        pytest.skip(f"{path} not built (needs the reference checkout: make -C oracle)")
+        pytest.skip(f"{path} not built (needs the reference checkout: make -C oracle REFERENCE=...)")
     return path
 
 
@@ -127,17 +127,18 @@ def test_gemm_wrappers_against_host_fp64(mode, tol):
 
 @pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])
 def test_loss_dropin_meets_the_reference_gate_in_fp32(tmp_path, case):
-    """oracle/_ref/parity_audit_all: the reference model with its attention kernels, its GEMM wrappers AND its loss
-    launcher (src/kernels/loss.cu) replaced - libb200loss behind the unchanged declaration of
-    include/kernels/loss.cuh. Loss, logits and every gradient (all of which flow from d_logits) still meet the gates
-    of scripts/compare_parity.py:108-117."""
+    """oracle/_ref/parity_audit_all: the reference model with its attention kernels, its GEMM wrappers, its loss
+    launcher (src/kernels/loss.cu) AND its LayerNorm launchers (src/kernels/layernorm.cu) replaced - libb200loss and
+    libb200norm behind the unchanged declarations of include/kernels/loss.cuh and layernorm.cuh. Loss, logits and
+    every gradient (all of which flow from d_logits, through five LayerNorms) still meet the gates of
+    scripts/compare_parity.py:108-117."""
     exe = _binary("parity_audit_all")
     work = tmp_path / case
     shutil.copytree(os.path.join(GOLDEN_DIR, case), work)
     env = dict(os.environ, B200ATTN_MATH="fp32", B200GEMM_MATH="fp32")
     res = subprocess.run([exe, str(work), "--tiled_attn"], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout + res.stderr
-    for tag in ("[b200attn]", "b200gemm:", "[b200loss]"):
+    for tag in ("[b200attn]", "b200gemm:", "[b200loss]", "[b200norm]"):
         assert tag not in res.stderr
     load = lambda n: np.fromfile(os.path.join(work, n), dtype=np.float32)
     assert _max_abs(load("cuda_logits.bin"), load("pytorch_logits.bin")) <= 1e-5
@@ -156,3 +157,24 @@ def test_adamw_dropin_against_host_restatement():
     assert "[b200opt]" not in res.stderr
     rep = json.loads(res.stdout.strip().splitlines()[-1])
     assert rep["ok"] and rep["max_abs_param_error"] <= 2e-6 and rep["max_abs_leftover_grad"] == 0.0
+
+
+def test_reference_kernel_test_suite_with_the_layernorm_dropin():
+    """tests/test_kernels.cu of the reference, unchanged, with src/kernels/layernorm.cu replaced by libb200norm as well
+    as attention.cu by libb200attn: its LayerNorm test (:13-89) and every other test pass."""
+    res = subprocess.run([_binary("test_kernels_all")], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "All isolated kernel tests passed" in res.stdout
+    assert "[b200norm]" not in res.stderr and "[b200attn]" not in res.stderr
+
+
+def test_layernorm_dropin_against_host_restatement():
+    """oracle/_ref/layernorm_check: both launchers of include/kernels/layernorm.cuh against a double-precision
+    restatement of src/kernels/layernorm.cu - register path (C = 128 k) and generic path, with and without gamma /
+    beta, residual_add and accumulate, dgamma / dbeta added to non-zero buffers."""
+    import json
+    res = subprocess.run([_binary("layernorm_check")], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "[b200norm]" not in res.stderr
+    cases = [json.loads(l) for l in res.stdout.splitlines() if l.startswith("{")]
+    assert len(cases) == 7 and all(c["ok"] for c in cases), res.stdout

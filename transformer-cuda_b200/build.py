@@ -1,7 +1,8 @@
 """Builds the engine in-tree with nvcc for sm_100a: lib/libb200attn.so (C ABI + the C++ launch API)
 and lib/libb200attn.a (the same objects, for static linking in place of the reference's
 src/kernels/attention.cu); beside them the drop-ins for the callers of the path: lib/libb200gemm.a
-(src/kernels/matmul.cu) and lib/libb200loss.so / .a (src/kernels/loss.cu). Rebuilds only when a source is newer than the library."""
+(src/kernels/matmul.cu), lib/libb200loss.so / .a (src/kernels/loss.cu) and lib/libb200norm.a
+(src/kernels/layernorm.cu). Rebuilds only when a source is newer than the library."""
 import os
 import shutil
 import subprocess
@@ -18,6 +19,7 @@ FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", 
 SO = os.path.join(LIBDIR, "libb200attn.so")
 AR = os.path.join(LIBDIR, "libb200attn.a")
 GEMM_AR = os.path.join(LIBDIR, "libb200gemm.a")
+NORM_AR = os.path.join(LIBDIR, "libb200norm.a")
 LOSS_SO = os.path.join(LIBDIR, "libb200loss.so")
 LOSS_AR = os.path.join(LIBDIR, "libb200loss.a")
 
@@ -91,6 +93,15 @@ def build(verbose=False, force=False, ptxas_info=False):
         if os.path.exists(LOSS_AR):
             os.remove(LOSS_AR)
         subprocess.check_call(["ar", "rcs", LOSS_AR, loss_obj])
+    # the LayerNorm drop-in (static library only: its interface is the C++ header of the reference)
+    norm_src = os.path.join(HERE, "norm", "layernorm_dropin.cu")
+    norm_obj = os.path.join(OBJDIR, "layernorm_dropin.o")
+    if force or _stale(norm_obj, [norm_src, os.path.join(HERE, "..", "include", "kernels", "layernorm.cuh")]):
+        subprocess.check_call([nvcc] + ARCH + FLAGS + ["--use_fast_math", "-I", os.path.join(HERE, "..", "include"), "-c", norm_src, "-o", norm_obj])
+    if force or _stale(NORM_AR, [norm_obj]):
+        if os.path.exists(NORM_AR):
+            os.remove(NORM_AR)
+        subprocess.check_call(["ar", "rcs", NORM_AR, norm_obj])
     return SO
 
 
