@@ -177,28 +177,62 @@ constexpr size_t kStagedWorkspace = size_t(64) << 20;
 inline int round_up_int(int x, int m) { return (x + m - 1) / m * m; }
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
-// FP32 (rows x cols, leading dimension ld_src) -> BF16 (rows_dst x ld_dst), everything outside rows x cols zeroed. One BF16
-// pair per thread: a warp reads 256 contiguous bytes and writes 128, whatever the alignment of the source rows.
+// FP32 (rows x cols, leading dimension ld_src) -> BF16 (rows_dst x ld_dst), everything outside rows x cols zeroed.
+// blockIdx.y walks rows, a thread converts eight consecutive columns into one 16-byte store (ld_dst is a multiple of 8
+// and the destination is 256-byte aligned); the source is read with two 16-byte loads when its row is aligned, else
+// with scalar loads (a warp still covers one contiguous 1 KB span, so every sector fetched is used).
 __global__ void __launch_bounds__(256) stage_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows,
                                                          int cols, long long ld_src, int rows_dst, int ld_dst) {
-    const int pairs_per_row = ld_dst / 2;
-    const long long g = blockIdx.x * 256ll + threadIdx.x;
-    if (g >= (long long)rows_dst * pairs_per_row) return;
-    const int r = int(g / pairs_per_row), c0 = int(g % pairs_per_row) * 2;
-    const float* s = src + (long long)r * ld_src + c0;
-    const float a = (r < rows && c0 < cols) ? __ldg(s) : 0.f;
-    const float b = (r < rows && c0 + 1 < cols) ? __ldg(s + 1) : 0.f;
-    *reinterpret_cast<__nv_bfloat162*>(dst + (long long)r * ld_dst + c0) = __floats2bfloat162_rn(a, b);
+    const int c0 = (blockIdx.x * 256 + threadIdx.x) * 8;
+    if (c0 >= ld_dst) return;
+    for (int r = blockIdx.y; r < rows_dst; r += gridDim.y) {
+        float v[8];
+        const float* s = src + (long long)r * ld_src + c0;
+        if (r < rows && c0 + 8 <= cols && (reinterpret_cast<uintptr_t>(s) & 15u) == 0) {
+            const float4 lo = __ldcs(reinterpret_cast<const float4*>(s)), hi = __ldcs(reinterpret_cast<const float4*>(s) + 1);
+            v[0] = lo.x, v[1] = lo.y, v[2] = lo.z, v[3] = lo.w, v[4] = hi.x, v[5] = hi.y, v[6] = hi.z, v[7] = hi.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (r < rows && c0 + j < cols) ? __ldcs(s + j) : 0.f;
+        }
+        uint4 out;
+        __nv_bfloat162 t;
+        t = __floats2bfloat162_rn(v[0], v[1]), out.x = *reinterpret_cast<unsigned int*>(&t);
+        t = __floats2bfloat162_rn(v[2], v[3]), out.y = *reinterpret_cast<unsigned int*>(&t);
+        t = __floats2bfloat162_rn(v[4], v[5]), out.z = *reinterpret_cast<unsigned int*>(&t);
+        t = __floats2bfloat162_rn(v[6], v[7]), out.w = *reinterpret_cast<unsigned int*>(&t);
+        *reinterpret_cast<uint4*>(dst + (long long)r * ld_dst + c0) = out;
+    }
+}
+void launch_stage_bf16(const float* src, __nv_bfloat16* dst, int rows, int cols, long long ld_src, int rows_dst, int ld_dst,
+                       cudaStream_t stream) {
+    const dim3 grid((ld_dst / 8 + 255) / 256, rows_dst < 32768 ? rows_dst : 32768);
+    stage_bf16_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, rows_dst, ld_dst);
 }
 
-// FP32 (rows x cols, padded leading dimension ld_src) -> FP32 (rows x cols, leading dimension ld_dst); one element per
-// thread, so loads and stores are both contiguous per warp.
+// FP32 (rows x cols, padded leading dimension ld_src, 16-byte aligned rows) -> FP32 (rows x cols, leading dimension
+// ld_dst, rows at any 4-byte phase). blockIdx.y walks rows; a thread writes one 16-byte aligned group of the
+// DESTINATION row (the up to three elements in front of the first aligned group and behind the last one are written
+// singly) and reads its four source elements with scalar loads: neighbouring threads read neighbouring 16 bytes, so
+// the loads of a warp cover one contiguous span as well.
 __global__ void __launch_bounds__(256) unpad_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols,
                                                         int ld_src, long long ld_dst) {
-    const long long g = blockIdx.x * 256ll + threadIdx.x;
-    if (g >= (long long)rows * cols) return;
-    const int r = int(g / cols), c = int(g % cols);
-    dst[(long long)r * ld_dst + c] = __ldg(src + (long long)r * ld_src + c);
+    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+        const float* s = src + (long long)r * ld_src;
+        float* d = dst + (long long)r * ld_dst;
+        const int head = (int)((4 - ((reinterpret_cast<uintptr_t>(d) >> 2) & 3)) & 3);  // elements before the first aligned group
+        const int c = head + (blockIdx.x * 256 + threadIdx.x) * 4;
+        if (blockIdx.x == 0 && threadIdx.x < head && (int)threadIdx.x < cols) d[threadIdx.x] = __ldcs(s + threadIdx.x);
+        if (c + 4 <= cols) {
+            *reinterpret_cast<float4*>(d + c) = make_float4(__ldcs(s + c), __ldcs(s + c + 1), __ldcs(s + c + 2), __ldcs(s + c + 3));
+        } else {
+            for (int j = c; j < cols; ++j) d[j] = __ldcs(s + j);
+        }
+    }
+}
+void launch_unpad_f32(const float* src, float* dst, int rows, int cols, int ld_src, long long ld_dst, cudaStream_t stream) {
+    const dim3 grid((cols / 4 + 1 + 255) / 256, rows < 32768 ? rows : 32768);
+    unpad_f32_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst);
 }
 
 bool wants_staging(int M, int N, int K, bool transA, bool transB, float beta) {
@@ -259,9 +293,8 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     const Plan& plan = it->second;
     if (!plan.has_algo) return false;
 
-    const long long ga = (long long)rowsA_p * (lda_p / 2), gb = (long long)rowsB_p * (ldb_p / 2);
-    stage_bf16_kernel<<<(unsigned int)((ga + 255) / 256), 256, 0, stream>>>(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p);
-    stage_bf16_kernel<<<(unsigned int)((gb + 255) / 256), 256, 0, stream>>>(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p);
+    launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
+    launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
     const float beta = 0.0f;
     const cublasStatus_t st = cublasLtMatmul(g_own_lt, plan.op, &alpha, Bb, plan.a, Ab, plan.b, &beta, Cp, plan.c, Cp, plan.c,
                                              &plan.algo, workspace, kStagedWorkspace, stream);
@@ -270,8 +303,7 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
         return false;
     }
     if (pad_c) {
-        const long long gc = (long long)M * N;
-        unpad_f32_kernel<<<(unsigned int)((gc + 255) / 256), 256, 0, stream>>>(Cp, C, M, N, ldc_p, N);
+        launch_unpad_f32(Cp, C, M, N, ldc_p, N, stream);
     }
     return true;
 }
