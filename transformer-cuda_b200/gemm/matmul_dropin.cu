@@ -235,16 +235,28 @@ void launch_unpad_f32(const float* src, float* dst, int rows, int cols, int ld_s
     unpad_f32_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols, ld_src, ld_dst);
 }
 
+// In BF16 arithmetic every large product is staged (B200GEMM_STAGE=all, the default): handed FP32 operands, the library
+// runs TF32 kernels at half the BF16 rate (measured on the GPT-2-small step: layer GEMMs 12.5 ms as TF32, 6.1 ms as BF16
+// + 4.0 ms of conversion passes). B200GEMM_STAGE=unaligned stages only the products whose leading dimensions rule the
+// library's fast kernels out.
+bool stage_all() {
+    static const bool v = [] {
+        const char* e = getenv("B200GEMM_STAGE");
+        return !(e && !strcmp(e, "unaligned"));
+    }();
+    return v;
+}
 bool wants_staging(int M, int N, int K, bool transA, bool transB, float beta) {
     if (math_mode() != Math::kBf16 || beta != 0.0f) return false;
     const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
-    if (lda % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0) return false;
-    return (double)M * N * K >= double(1ull << 30);  // small products are not worth three extra passes
+    const bool aligned = lda % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0;
+    if (aligned && !stage_all()) return false;
+    return (double)M * N * K >= double(1ull << 30);  // small products are not worth the extra passes
 }
 
 // Returns false when the staged path could not run (the caller then takes the direct path).
 bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, int K, bool transA, bool transB, float alpha,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, cublasLtEpilogue_t epilogue = CUBLASLT_EPILOGUE_DEFAULT, const float* bias = nullptr) {
     std::lock_guard<std::mutex> lock(g_plans_mutex);
     if (!g_own_lt && cublasLtCreate(&g_own_lt) != CUBLAS_STATUS_SUCCESS) return false;
     // The library only picks its fast kernels when the problem dimensions themselves are multiples of 8, so
@@ -266,7 +278,9 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     __nv_bfloat16* Bb = reinterpret_cast<__nv_bfloat16*>(base + kStagedWorkspace + bytesA);
     float* Cp = pad_c ? reinterpret_cast<float*>(base + kStagedWorkspace + bytesA + bytesB) : C;
 
-    const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, -1};
+    const bool pad_any = pad_c || Kp != K;
+    if (epilogue != CUBLASLT_EPILOGUE_DEFAULT && pad_any) return false;  // epilogues only on products that need no padding
+    const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, (int)epilogue};
     auto it = g_staged_plans.find(key);
     if (it == g_staged_plans.end()) {
         Plan p;
@@ -275,6 +289,10 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
         if (ok) {
             cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &opB, sizeof(opB));
             cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &opA, sizeof(opA));
+            if (epilogue != CUBLASLT_EPILOGUE_DEFAULT) {
+                cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_EPILOGUE, &epilogue, sizeof(epilogue));
+                cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias));
+            }
             cublasLtMatrixLayoutCreate(&p.a, CUDA_R_16BF, ldb_p, rowsB_p, ldb_p);  // row-major B seen column-major
             cublasLtMatrixLayoutCreate(&p.b, CUDA_R_16BF, lda_p, rowsA_p, lda_p);
             cublasLtMatrixLayoutCreate(&p.c, CUDA_R_32F, Np, Mp, ldc_p);
@@ -292,6 +310,7 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     }
     const Plan& plan = it->second;
     if (!plan.has_algo) return false;
+    if (epilogue != CUBLASLT_EPILOGUE_DEFAULT) cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias));
 
     launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
     launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
@@ -335,8 +354,7 @@ void matmul_cublaslt(cublasLtHandle_t lt_handle, const float* A, const float* B,
                      cublasLtEpilogue_t epilogue, const float* bias, void* workspace, size_t workspace_size, bool transA,
                      bool transB, float alpha, float beta, cudaStream_t stream) {
     if (workspace == nullptr) workspace_size = 0;
-    if (epilogue == CUBLASLT_EPILOGUE_DEFAULT && bias == nullptr && wants_staging(M, N, K, transA, transB, beta) &&
-        staged_bf16_gemm(A, B, C, M, N, K, transA, transB, alpha, stream))
+    if (wants_staging(M, N, K, transA, transB, beta) && staged_bf16_gemm(A, B, C, M, N, K, transA, transB, alpha, stream, epilogue, bias))
         return;
     const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, (int)epilogue};
     Plan plan;
