@@ -691,7 +691,7 @@ def main():
                 "path": "pinned host BF16 q,k,v,dO -> device -> b200attn_fwd_bf16 + b200attn_bwd_bf16 -> host o,dq,dk,dv; "
                         "upload, kernels and download of consecutive steps overlap on three streams"},
         "gpu_launches": 4 * args.steps,  # per step: forward kernel, backward pre-pass, backward kernel, dQ convert
-        "roofline": {"bound": "tensor", "kernel": "attn_bwd_tc_kernel", "achieved": bwd_tf, "peak": peaks["bf16"],
+        "roofline": {"bound": "tensor", "kernel": "attn_bwd_tc64_kernel" if d == 64 else "attn_bwd_tc_kernel", "achieved": bwd_tf, "peak": peaks["bf16"],
                      "unit": UNIT, "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} (burst cuBLAS BF16)",
                      "traffic": ncu_traffic_per_launch(args.workload), "launch_ms": bwd_ms,
                      "timed_launches": kt["bwd_launches"],
