@@ -229,6 +229,43 @@ def run_gpt_step(args):
     print(json.dumps(line), flush=True)
 
 
+def time_loss_kernel(pkg, dev, peaks, rows, iters=10):
+    """The loss launcher at the head of the model's backward (cross_entropy_forward_backward, loss.cu:97) on `rows` rows
+    of the GPT step's vocabulary (16384 rows: 3.3 GB in, 3.3 GB out, far beyond L2): algorithmic bytes = 8 per logit."""
+    import importlib
+    import torch
+    loss_ops = importlib.import_module(pkg.__name__ + ".loss_ops")
+    V = 50257
+    logits = torch.randn(1, rows, V, device=dev)
+    targets = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
+    dlogits = torch.empty_like(logits)
+    for _ in range(3):
+        loss_ops.cross_entropy_forward_backward(logits, targets, dlogits=dlogits)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        loss_ops.cross_entropy_forward_backward(logits, targets, dlogits=dlogits)
+    e1.record()
+    torch.cuda.synchronize()
+    loss_ops.check_device_fault()
+    ms, nbytes = e0.elapsed_time(e1) / iters, 8 * rows * V
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"launcher": f"cross_entropy_forward_backward (rows={rows}, V={V})", "replaces": "loss.cu:97", "ms": round(ms, 4),
+            "algorithmic_bytes": nbytes, "achieved_gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm"], 3)}
+
+
+def run_loss_kernel(args):
+    import torch
+    import __graft_entry__ as entry
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    row = time_loss_kernel(entry.load_package(), dev, peaks, args.loss_rows, iters=max(1, min(args.steps, 10)))
+    print(json.dumps({"suite": "loss", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm"], "peak_source": peaks["source"], "kernels": [row]}),
+          flush=True)
+
+
 def run_path_kernels(args, B, H, T, d):
     """The HBM-bound launchers of the path (and the FP32 parity kernels) on the workload's shape, one GPU:
     achieved GB/s = algorithmic bytes / CUDA-event time, against the measured HBM copy bandwidth."""
@@ -333,17 +370,7 @@ def run_path_kernels(args, B, H, T, d):
     ms_chain = timed(chain_step, copies)
     del pq, pdo, pout, pdqkv, qkv, q32, k32, v32, qb, kb, vb, merged, scores, probs
     torch.cuda.empty_cache()
-    # the loss launcher at the head of the model's backward, on the GPT step's shape (3.3 GB in, 3.3 GB out: beyond L2)
-    import importlib
-    loss_ops = importlib.import_module(pkg.__name__ + ".loss_ops")
-    cB, cT, cV = 16, 1024, 50257
-    logits = torch.randn(cB, cT, cV, device=dev)
-    targets = torch.randint(0, cV, (cB * cT,), device=dev, dtype=torch.int32)
-    dlogits = torch.empty_like(logits)
-    iters = 10
-    ms = timed(lambda c: loss_ops.cross_entropy_forward_backward(logits, targets, dlogits=dlogits))
-    loss_ops.check_device_fault()
-    row(f"cross_entropy_forward_backward (rows={cB * cT}, V={cV})", "loss.cu:97", ms, 8 * cB * cT * cV)
+    out.append(time_loss_kernel(pkg, dev, peaks, args.loss_rows))
     print(json.dumps({
         "suite": "path-kernels", "unit": "GB/s", "hbm_peak_gbs": peaks["hbm"], "peak_source": peaks["source"],
         "config": {"workload": workload_name(args, B, H, T, d), "l2": f"{copies} rotating buffer sets"},
@@ -499,7 +526,8 @@ def main():
     ap.add_argument("--extra", default="c3,c5_512,c5_1024,c5_2048,c5_4096,c5_8192,c5_16384",
                     help="comma-separated other workloads measured briefly (device-timed) after the main one and reported "
                          "under `extra`; empty string: none")
-    ap.add_argument("--suite", default="attention", choices=["attention", "path-kernels"],
+    ap.add_argument("--loss-rows", type=int, default=16384, help="rows of 50257 logits for the loss-kernel timing")
+    ap.add_argument("--suite", default="attention", choices=["attention", "path-kernels", "loss"],
                     help="'path-kernels': time every other launcher of the path (layout, softmax, pre-pass, FP32 parity "
                          "kernels) against the HBM roofline and print one JSON line with a table")
     args = ap.parse_args()
@@ -514,6 +542,9 @@ def main():
         return
     if args.suite == "path-kernels":
         run_path_kernels(args, B, H, T, d)
+        return
+    if args.suite == "loss":
+        run_loss_kernel(args)
         return
 
     import torch

@@ -53,6 +53,13 @@ int main(int argc, char** argv) {
         {"head_dw_unaligned", 768, 50257, 2048, true, false, 1.0f, 0.0f, 1},          // dW = X^T dlogits
         {"head_dx_unaligned", 2048, 768, 50257, false, true, 1.0f, 0.0f, 0},          // dX = dlogits W^T
         {"unaligned_small", 33, 77, 45, false, true, 1.0f, 0.0f, 0},
+        // large aligned and ragged products in all four operand layouts: staged in BF16 arithmetic, and with
+        // B200GEMM_KERNEL=tcgen05 multiplied by the hand-written kernel (each has at least 120 output tiles of 128 x 256)
+        {"layer_nn", 4096, 3072, 768, false, false, 1.0f, 0.0f, 1},
+        {"layer_nt", 4096, 3072, 768, false, true, 1.0f, 0.0f, 1},
+        {"ragged_tn", 2000, 3000, 1000, true, false, 0.5f, 0.0f, 0},
+        {"ragged_tt", 2000, 3000, 1000, true, true, 1.0f, 0.0f, 0},
+        {"ragged_unaligned_nn", 1999, 3001, 777, false, false, 1.0f, 0.0f, 1},
     };
     bool all_ok = true;
     for (const Case& c : cases) {
@@ -128,5 +135,7 @@ int main(int argc, char** argv) {
         all_ok = all_ok && ok;
         printf("{\"case\": \"bias_helpers\", \"bias_backward_max_abs\": %.3e, \"add_bias_max_abs\": %.3e, \"ok\": %s}\n", e1, e2, ok ? "true" : "false");
     }
-    return all_ok ? 0 : 1;
+    const int fault = b200gemm_check_device_fault();
+    printf("{\"tcgen05_kernel_launches\": %lld, \"device_fault\": %d}\n", b200gemm_tc_launches(), fault);
+    return (all_ok && fault == 0) ? 0 : 1;
 }

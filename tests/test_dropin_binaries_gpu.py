@@ -112,17 +112,23 @@ def test_gemm_dropin_on_the_tensor_cores(tmp_path):
     assert _max_abs(got, ref) <= 2e-2
 
 
-@pytest.mark.parametrize("mode,tol", [("fp32", "1e-4"), ("bf16", "2e-2")])
-def test_gemm_wrappers_against_host_fp64(mode, tol):
+@pytest.mark.parametrize("mode,tol,kernel", [("fp32", "1e-4", "library"), ("bf16", "2e-2", "library"), ("bf16", "2e-2", "tcgen05")])
+def test_gemm_wrappers_against_host_fp64(mode, tol, kernel):
     """oracle/_ref/gemm_check: every wrapper of include/kernels/matmul.cuh on seeded inputs against an FP64 host
     computation, including the language-model-head shapes (V = 50257: leading dimensions that are not a
     multiple of 16 bytes), which in BF16 arithmetic take the staged path (padded BF16 operands, padded FP32
-    result copied into place)."""
-    res = subprocess.run([_binary("gemm_check"), tol], capture_output=True, text=True, timeout=600,
-                         env=dict(os.environ, B200GEMM_MATH=mode))
+    result copied into place), or - B200GEMM_KERNEL=tcgen05 - the hand-written tcgen05 kernel of gemm/gemm_tc.cu, which
+    writes the unaligned result in place; large products in all four operand layouts, ragged sizes included."""
+    res = subprocess.run([_binary("gemm_check"), tol], capture_output=True, text=True, timeout=900,
+                         env=dict(os.environ, B200GEMM_MATH=mode, B200GEMM_KERNEL=kernel))
     assert res.returncode == 0, res.stdout + res.stderr
     assert "b200gemm:" not in res.stderr
-    assert res.stdout.count('"ok": true') == 8, res.stdout
+    assert res.stdout.count('"ok": true') == 13 and '"ok": false' not in res.stdout, res.stdout
+    import json
+    tail = json.loads(res.stdout.strip().splitlines()[-1])
+    assert tail["device_fault"] == 0
+    # seven of the cases are large enough for the hand-written kernel; without the switch it never runs
+    assert tail["tcgen05_kernel_launches"] == (7 if kernel == "tcgen05" else 0), tail
 
 
 @pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])

@@ -70,16 +70,21 @@ def build(verbose=False, force=False, ptxas_info=False):
         if os.path.exists(AR):
             os.remove(AR)
         subprocess.check_call(["ar", "rcs", AR] + objs)
-    # the GEMM drop-in for the reference model (links against cuBLAS, so it stays out of libb200attn)
-    gemm_src = os.path.join(HERE, "gemm", "matmul_dropin.cu")
-    gemm_obj = os.path.join(OBJDIR, "matmul_dropin.o")
-    gemm_hdr = os.path.join(HERE, "..", "include", "kernels", "matmul.cuh")
-    if force or _stale(gemm_obj, [gemm_src, gemm_hdr]):
-        subprocess.check_call([nvcc] + ARCH + FLAGS + ["-I", os.path.join(HERE, "..", "include"), "-c", gemm_src, "-o", gemm_obj])
-    if force or _stale(GEMM_AR, [gemm_obj]):
+    # the GEMM drop-in for the reference model (links against cuBLAS, so it stays out of libb200attn): the wrappers and
+    # the hand-written tcgen05 GEMM they can route staged products to
+    gemm_objs = []
+    gemm_hdrs = [os.path.join(HERE, "..", "include", "kernels", "matmul.cuh"), os.path.join(HERE, "gemm", "gemm_tc.h"),
+                 os.path.join(CSRC, "tc_common.cuh")]
+    for name in ("matmul_dropin", "gemm_tc"):
+        src = os.path.join(HERE, "gemm", name + ".cu")
+        obj = os.path.join(OBJDIR, name + ".o")
+        gemm_objs.append(obj)
+        if force or _stale(obj, [src] + gemm_hdrs):
+            subprocess.check_call([nvcc] + ARCH + FLAGS + ["-I", os.path.join(HERE, "..", "include"), "-I", CSRC, "-c", src, "-o", obj])
+    if force or _stale(GEMM_AR, gemm_objs):
         if os.path.exists(GEMM_AR):
             os.remove(GEMM_AR)
-        subprocess.check_call(["ar", "rcs", GEMM_AR, gemm_obj])
+        subprocess.check_call(["ar", "rcs", GEMM_AR] + gemm_objs)
     # the loss drop-in (fused softmax cross-entropy): its own shared + static library, no dependency on the attention engine
     loss_src = os.path.join(HERE, "loss", "cross_entropy.cu")
     loss_obj = os.path.join(OBJDIR, "cross_entropy.o")

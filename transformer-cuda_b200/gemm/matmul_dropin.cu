@@ -10,6 +10,8 @@
 
 #include <cuda_bf16.h>
 
+#include "gemm_tc.h"
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -246,6 +248,15 @@ bool stage_all() {
     }();
     return v;
 }
+bool use_tc_kernel() {
+    static const bool v = [] {
+        const char* e = getenv("B200GEMM_KERNEL");
+        return e && !strcmp(e, "tcgen05");
+    }();
+    return v;
+}
+constexpr int kMinTcTiles = 120;
+
 bool wants_staging(int M, int N, int K, bool transA, bool transB, float beta) {
     if (math_mode() != Math::kBf16 || beta != 0.0f) return false;
     const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
@@ -280,6 +291,14 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
 
     const bool pad_any = pad_c || Kp != K;
     if (epilogue != CUBLASLT_EPILOGUE_DEFAULT && pad_any) return false;  // epilogues only on products that need no padding
+    // B200GEMM_KERNEL=tcgen05: the hand-written kernel (gemm_tc.cu) multiplies the staged operands and writes C in place,
+    // whatever its leading dimension (no padded result tile, no copy back). Products with fewer output tiles than SMs
+    // stay with the library, which splits K for them.
+    if (use_tc_kernel() && epilogue == CUBLASLT_EPILOGUE_DEFAULT && b200gemm::tc_gemm_tiles(M, N) >= kMinTcTiles) {
+        launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
+        launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
+        if (b200gemm::tc_gemm_bf16(Ab, rowsA_p, lda_p, transA, Bb, rowsB_p, ldb_p, transB, C, N, M, N, Kp, alpha, stream)) return true;
+    }
     const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, (int)epilogue};
     auto it = g_staged_plans.find(key);
     if (it == g_staged_plans.end()) {
@@ -328,6 +347,16 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
 }
 
 }  // namespace
+
+extern "C" long long b200gemm_tc_launches(void) { return b200gemm::tc_gemm_launches(); }
+
+extern "C" int b200gemm_check_device_fault(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+    const unsigned int word = b200gemm::tc_gemm_take_fault();
+    if (word == 0) return 0;
+    fprintf(stderr, "b200gemm: a bounded wait ran out inside the tcgen05 GEMM kernel (record 0x%08x)\n", word);
+    return -3;
+}
 
 void matmul_forward(cublasHandle_t handle, const float* A, const float* B, float* C, int M, int N, int K, bool transA,
                     bool transB, float alpha, float beta, cudaStream_t stream) {
