@@ -112,7 +112,7 @@ def test_gemm_dropin_on_the_tensor_cores(tmp_path):
     assert _max_abs(got, ref) <= 2e-2
 
 
-@pytest.mark.parametrize("mode,tol,kernel", [("fp32", "1e-4", "library"), ("bf16", "2e-2", "library"), ("bf16", "2e-2", "tcgen05")])
+@pytest.mark.parametrize("mode,tol,kernel", [("fp32", "1e-4", "library"), ("bf16", "2e-2", "library"), ("bf16", "2e-2", "tcgen05"), ("bf16", "2e-2", "auto")])
 def test_gemm_wrappers_against_host_fp64(mode, tol, kernel):
     """oracle/_ref/gemm_check: every wrapper of include/kernels/matmul.cuh on seeded inputs against an FP64 host
     computation, including the language-model-head shapes (V = 50257: leading dimensions that are not a
@@ -127,8 +127,8 @@ def test_gemm_wrappers_against_host_fp64(mode, tol, kernel):
     import json
     tail = json.loads(res.stdout.strip().splitlines()[-1])
     assert tail["device_fault"] == 0
-    # seven of the cases are large enough for the hand-written kernel; without the switch it never runs
-    assert tail["tcgen05_kernel_launches"] == (7 if kernel == "tcgen05" else 0), tail
+    # seven of the cases are large enough for the hand-written kernel; "library" never runs it
+    assert tail["tcgen05_kernel_launches"] == {"tcgen05": 7, "auto": 2, "library": 0}[kernel], tail
 
 
 @pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])

@@ -40,7 +40,7 @@ constexpr int kBBytes = kBN * kBK * 2;      // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAtom64Bytes = 64 * 128;      // a 64-row x 64-element box: 8 KB
 constexpr int kEpiWarps = 4;
-constexpr int kEpiPitch = 33;               // floats per staged row: conflict-free transposition
+constexpr int kEpiPitch = 36;               // floats per staged row: 16-byte stores and conflict-free column reads
 constexpr int kEpiBytes = kEpiWarps * 32 * kEpiPitch * 4;
 constexpr int kProducerWarp = 4, kMmaWarp = 5;
 constexpr int kThreads = 192;
@@ -157,14 +157,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     mbar_arrive(&acc_empty[buf]);
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) stage[lane * kEpiPitch + j] = __uint_as_float(v[j]) * a.alpha;
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float4*>(stage + lane * kEpiPitch + 4 * j) =
+                        make_float4(__uint_as_float(v[4 * j]) * a.alpha, __uint_as_float(v[4 * j + 1]) * a.alpha,
+                                    __uint_as_float(v[4 * j + 2]) * a.alpha, __uint_as_float(v[4 * j + 3]) * a.alpha);
                 __syncwarp();
+                float o[32];
+#pragma unroll
+                for (int r = 0; r < 32; ++r) o[r] = stage[r * kEpiPitch + lane];
                 const int col = n0 + c * 32 + lane;
-                if (col < a.N) {
-                    const int rows = min(32, a.M - m0);
-                    float* dst = a.C + (long long)m0 * a.ldc + col;
-                    for (int r = 0; r < rows; ++r) dst[(long long)r * a.ldc] = stage[r * kEpiPitch + lane];
-                }
+                const int rows = col < a.N ? a.M - m0 : 0;  // rows of this warp's strip that exist (may exceed 32)
+                float* dst = a.C + (long long)m0 * a.ldc + col;
+#pragma unroll
+                for (int r = 0; r < 32; ++r)
+                    if (r < rows) dst[(long long)r * a.ldc] = o[r];
                 __syncwarp();
             }
         }

@@ -248,14 +248,31 @@ bool stage_all() {
     }();
     return v;
 }
-bool use_tc_kernel() {
-    static const bool v = [] {
+// Which staged products go to the hand-written tcgen05 kernel (gemm_tc.cu) instead of the library:
+//   B200GEMM_KERNEL=auto (default)  those it wins: a result with an unaligned leading dimension that is larger than the
+//                                   operands (the language-model-head forward: 3.3 GB of logits written in place instead
+//                                   of into a padded tile and copied; measured 1.73 against 2.20 ms)
+//   B200GEMM_KERNEL=tcgen05         every staged product with at least 120 output tiles and no epilogue
+//   B200GEMM_KERNEL=library         none
+// Elsewhere the library's two-CTA kernels are faster: a one-CTA kernel with both operands in shared memory moves 96 KB
+// through the 128 B/clk port per 512 cycles of MMA (fill + read) and re-reads its operands from L2 for every tile;
+// measured 540-740 TFLOP/s against 750-1100 for the library on the layer shapes.
+enum class TcPolicy { kAuto, kAlways, kNever };
+TcPolicy tc_policy() {
+    static const TcPolicy v = [] {
         const char* e = getenv("B200GEMM_KERNEL");
-        return e && !strcmp(e, "tcgen05");
+        if (e && !strcmp(e, "tcgen05")) return TcPolicy::kAlways;
+        if (e && !strcmp(e, "library")) return TcPolicy::kNever;
+        return TcPolicy::kAuto;
     }();
     return v;
 }
 constexpr int kMinTcTiles = 120;
+bool use_tc_kernel(int M, int N, int K, bool unaligned_result) {
+    if (tc_policy() == TcPolicy::kNever || b200gemm::tc_gemm_tiles(M, N) < kMinTcTiles) return false;
+    if (tc_policy() == TcPolicy::kAlways) return true;
+    return unaligned_result && (double)M * N >= (double)K * ((double)M + N);
+}
 
 bool wants_staging(int M, int N, int K, bool transA, bool transB, float beta) {
     if (math_mode() != Math::kBf16 || beta != 0.0f) return false;
@@ -291,10 +308,9 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
 
     const bool pad_any = pad_c || Kp != K;
     if (epilogue != CUBLASLT_EPILOGUE_DEFAULT && pad_any) return false;  // epilogues only on products that need no padding
-    // B200GEMM_KERNEL=tcgen05: the hand-written kernel (gemm_tc.cu) multiplies the staged operands and writes C in place,
-    // whatever its leading dimension (no padded result tile, no copy back). Products with fewer output tiles than SMs
-    // stay with the library, which splits K for them.
-    if (use_tc_kernel() && epilogue == CUBLASLT_EPILOGUE_DEFAULT && b200gemm::tc_gemm_tiles(M, N) >= kMinTcTiles) {
+    // the hand-written kernel multiplies the staged operands and writes C in place, whatever its leading dimension (no
+    // padded result tile, no copy back); products with fewer output tiles than SMs stay with the library, which splits K
+    if (epilogue == CUBLASLT_EPILOGUE_DEFAULT && use_tc_kernel(M, N, K, pad_c)) {
         launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
         launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
         if (b200gemm::tc_gemm_bf16(Ab, rowsA_p, lda_p, transA, Bb, rowsB_p, ldb_p, transB, C, N, M, N, Kp, alpha, stream)) return true;
