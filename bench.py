@@ -193,6 +193,8 @@ def run_gpt_step(args):
     env.setdefault("B200ATTN_FUSED_CONVERT", "1")  # BF16 copies of q, k, v, dO come out of the layout launchers
     if args.gemm != "reference":
         env["B200GEMM_MATH"] = args.gemm
+        # the reference model never rewrites a gradient between the dW and dX products that read it (src/model.cu:451-700)
+        env.setdefault("B200GEMM_REUSE_STAGED", "1")
     res = subprocess.run([exe, "--steps", str(steps), "--warmup", str(min(args.warmup, 3))], env=env, capture_output=True, text=True)
     if res.returncode != 0:
         raise SystemExit(f"{name} failed on rank {rank}: {res.stderr[-2000:]}")

@@ -63,6 +63,7 @@ int main(int argc, char** argv) {
     };
     bool all_ok = true;
     for (const Case& c : cases) {
+        b200gemm_forget_staged();  // every case fills fresh buffers, possibly at the addresses of the previous case's
         const size_t na = size_t(c.M) * c.K, nb = size_t(c.K) * c.N, nc = size_t(c.M) * c.N;
         std::vector<float> A(na), B(nb), C0(nc), bias(c.N), C(nc);
         for (auto& x : A) x = next_uniform();
@@ -134,6 +135,41 @@ int main(int argc, char** argv) {
         const bool ok = e1 <= 1e-3 && e2 <= 1e-6;
         all_ok = all_ok && ok;
         printf("{\"case\": \"bias_helpers\", \"bias_backward_max_abs\": %.3e, \"add_bias_max_abs\": %.3e, \"ok\": %s}\n", e1, e2, ok ? "true" : "false");
+    }
+    // the backward pair dW = X^T dY, dX = dY W^T: with B200GEMM_REUSE_STAGED=1 the second call takes dY's BF16 copy from the first
+    {
+        const int R = 4096, C1 = 768, C2 = 3072;
+        std::vector<float> X(size_t(R) * C1), dY(size_t(R) * C2), W(size_t(C1) * C2), dX(size_t(R) * C1);
+        for (auto& x : X) x = next_uniform();
+        for (auto& x : dY) x = next_uniform();
+        for (auto& x : W) x = next_uniform();
+        float *dXa, *ddY, *dW, *ddW, *ddX;
+        CK(cudaMalloc(&dXa, X.size() * 4)); CK(cudaMalloc(&ddY, dY.size() * 4)); CK(cudaMalloc(&dW, W.size() * 4));
+        CK(cudaMalloc(&ddW, W.size() * 4)); CK(cudaMalloc(&ddX, dX.size() * 4));
+        CK(cudaMemcpy(dXa, X.data(), X.size() * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(ddY, dY.data(), dY.size() * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(dW, W.data(), W.size() * 4, cudaMemcpyHostToDevice));
+        const long long before = b200gemm_staged_reuses();
+        matmul_cublaslt(lt, dXa, ddY, ddW, C1, C2, R, CUBLASLT_EPILOGUE_DEFAULT, nullptr, workspace, ws_bytes, true, false, 1.0f, 0.0f, 0);
+        matmul_cublaslt(lt, ddY, dW, ddX, R, C1, C2, CUBLASLT_EPILOGUE_DEFAULT, nullptr, workspace, ws_bytes, false, true, 1.0f, 0.0f, 0);
+        CK(cudaDeviceSynchronize());
+        CK(cudaMemcpy(dX.data(), ddX, dX.size() * 4, cudaMemcpyDeviceToHost));
+        double max_rel = 0.0;
+        for (int s = 0; s < 2000; ++s) {
+            const int i = int((next_uniform() * 0.5f + 0.5f) * R) % R, j = int((next_uniform() * 0.5f + 0.5f) * C1) % C1;
+            double acc = 0.0, scale = 0.0;
+            for (int k = 0; k < C2; ++k) {
+                const double p = double(dY[size_t(i) * C2 + k]) * W[size_t(j) * C2 + k];
+                acc += p, scale += fabs(p);
+            }
+            const double rel = fabs(double(dX[size_t(i) * C1 + j]) - acc) / (scale / sqrt(double(C2)) + 1.0);
+            if (!(rel <= max_rel)) max_rel = rel;
+        }
+        const bool ok = max_rel <= tol;
+        all_ok = all_ok && ok;
+        printf("{\"case\": \"backward_pair_dx\", \"max_rel\": %.3e, \"staged_reuses\": %lld, \"ok\": %s}\n", max_rel,
+               b200gemm_staged_reuses() - before, ok ? "true" : "false");
+        cudaFree(dXa); cudaFree(ddY); cudaFree(dW); cudaFree(ddW); cudaFree(ddX);
     }
     const int fault = b200gemm_check_device_fault();
     printf("{\"tcgen05_kernel_launches\": %lld, \"device_fault\": %d}\n", b200gemm_tc_launches(), fault);

@@ -123,12 +123,24 @@ def test_gemm_wrappers_against_host_fp64(mode, tol, kernel):
                          env=dict(os.environ, B200GEMM_MATH=mode, B200GEMM_KERNEL=kernel))
     assert res.returncode == 0, res.stdout + res.stderr
     assert "b200gemm:" not in res.stderr
-    assert res.stdout.count('"ok": true') == 13 and '"ok": false' not in res.stdout, res.stdout
+    assert res.stdout.count('"ok": true') == 14 and '"ok": false' not in res.stdout, res.stdout
     import json
     tail = json.loads(res.stdout.strip().splitlines()[-1])
     assert tail["device_fault"] == 0
     # seven of the cases are large enough for the hand-written kernel; "library" never runs it
     assert tail["tcgen05_kernel_launches"] == {"tcgen05": 7, "auto": 2, "library": 0}[kernel], tail
+
+
+def test_staged_operand_reuse_between_the_backward_pair():
+    """B200GEMM_REUSE_STAGED=1: dW = X^T dY followed by dX = dY W^T converts dY once; dX still agrees with the FP64 host
+    result (the last case of gemm_check), and without the switch nothing is reused."""
+    import json
+    for flag, want in (("1", 1), ("0", 0)):
+        res = subprocess.run([_binary("gemm_check"), "2e-2"], capture_output=True, text=True, timeout=900,
+                             env=dict(os.environ, B200GEMM_MATH="bf16", B200GEMM_REUSE_STAGED=flag))
+        assert res.returncode == 0, res.stdout + res.stderr
+        pair = [json.loads(l) for l in res.stdout.splitlines() if "backward_pair_dx" in l][0]
+        assert pair["ok"] and pair["staged_reuses"] == want, pair
 
 
 @pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])

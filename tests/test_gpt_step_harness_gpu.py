@@ -65,6 +65,16 @@ def test_every_dropin_together_follows_the_same_loss_curve():
     assert abs(got["loss"] - ref["loss"]) <= 1e-4 * max(1.0, abs(ref["loss"])), (got["loss"], ref["loss"])
 
 
+def test_reusing_staged_gradients_does_not_change_the_step():
+    """B200GEMM_REUSE_STAGED=1 on the reference model (its backward never rewrites a gradient between the dW and dX
+    products that read it): same loss after three steps as with every operand converted afresh (BF16 arithmetic; the
+    small model's products are below the staging threshold unless forced, so the threshold is lowered for this test)."""
+    env = {"B200ATTN_MATH": "bf16", "B200GEMM_MATH": "bf16", "B200GEMM_STAGE_MIN_MACS": "1"}
+    ref = _run(_binary("gpt_step_dp_b200_all"), dict(env, B200GEMM_REUSE_STAGED="0"))
+    got = _run(_binary("gpt_step_dp_b200_all"), dict(env, B200GEMM_REUSE_STAGED="1"))
+    assert abs(got["loss"] - ref["loss"]) <= 2e-3 * max(1.0, abs(ref["loss"])), (got["loss"], ref["loss"])
+
+
 def test_two_ranks_average_their_gradients():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

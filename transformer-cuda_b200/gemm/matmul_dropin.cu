@@ -274,13 +274,44 @@ bool use_tc_kernel(int M, int N, int K, bool unaligned_result) {
     return unaligned_result && (double)M * N >= (double)K * ((double)M + N);
 }
 
+// Products below this many multiply-adds are never staged (B200GEMM_STAGE_MIN_MACS overrides the default 2^30, for tests
+// that want the staged path on small shapes).
+double stage_min_macs() {
+    static const double v = [] {
+        const char* e = getenv("B200GEMM_STAGE_MIN_MACS");
+        return e ? atof(e) : double(1ull << 30);
+    }();
+    return v;
+}
 bool wants_staging(int M, int N, int K, bool transA, bool transB, float beta) {
     if (math_mode() != Math::kBf16 || beta != 0.0f) return false;
     const int lda = transA ? M : K, ldb = transB ? K : N, ldc = N;
     const bool aligned = lda % 4 == 0 && ldb % 4 == 0 && ldc % 4 == 0 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0;
     if (aligned && !stage_all()) return false;
-    return (double)M * N * K >= double(1ull << 30);  // small products are not worth the extra passes
+    return (double)M * N * K >= stage_min_macs();  // small products are not worth the extra passes
 }
+
+// B200GEMM_REUSE_STAGED=1: the BF16 copy of the B operand of a staged product is kept, and when the NEXT staged product
+// reads the same matrix (same address, same shape) as its A operand the copy is used instead of converting it again. That
+// is the pattern of a backward pass - dW = X^T dY followed by dX = dY W^T (src/model.cu:451-476 and every layer) - where the
+// conversion of dY (3.3 GB at the language-model head) is otherwise paid twice. Off by default: the caller has to guarantee
+// that a matrix is not rewritten between two consecutive GEMM calls that both read it. Only B -> A of the very next call
+// is matched, so weights (always B, rewritten by the optimizer between steps) are never taken from a kept copy.
+bool reuse_staged() {
+    static const bool v = [] {
+        const char* e = getenv("B200GEMM_REUSE_STAGED");
+        return e && !strcmp(e, "1");
+    }();
+    return v;
+}
+struct KeptOperand {
+    Scratch buf;
+    const void* src = nullptr;
+    int rows = 0, cols = 0;
+    long long call = -1;  // index of the staged call that wrote it
+};
+KeptOperand g_kept[2];
+long long g_staged_calls = 0, g_staged_reused = 0;
 
 // Returns false when the staged path could not run (the caller then takes the direct path).
 bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, int K, bool transA, bool transB, float alpha,
@@ -305,14 +336,26 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     __nv_bfloat16* Ab = reinterpret_cast<__nv_bfloat16*>(base + kStagedWorkspace);
     __nv_bfloat16* Bb = reinterpret_cast<__nv_bfloat16*>(base + kStagedWorkspace + bytesA);
     float* Cp = pad_c ? reinterpret_cast<float*>(base + kStagedWorkspace + bytesA + bytesB) : C;
+    bool a_ready = false, b_ready = false;
+    const long long call = g_staged_calls++;
+    if (reuse_staged()) {
+        int a_slot = -1;
+        for (int i = 0; i < 2; ++i)
+            if (g_kept[i].src == A && g_kept[i].rows == rowsA && g_kept[i].cols == colsA && g_kept[i].call == call - 1) a_slot = i;
+        if (a_slot >= 0) Ab = static_cast<__nv_bfloat16*>(g_kept[a_slot].buf.p), a_ready = true, ++g_staged_reused;
+        KeptOperand& keep = g_kept[a_slot >= 0 ? 1 - a_slot : int(call & 1)];
+        keep.src = nullptr;
+        if (void* kb = keep.buf.get(bytesB)) Bb = static_cast<__nv_bfloat16*>(kb), keep.src = B, keep.rows = rowsB, keep.cols = colsB, keep.call = call;
+    }
 
     const bool pad_any = pad_c || Kp != K;
     if (epilogue != CUBLASLT_EPILOGUE_DEFAULT && pad_any) return false;  // epilogues only on products that need no padding
     // the hand-written kernel multiplies the staged operands and writes C in place, whatever its leading dimension (no
     // padded result tile, no copy back); products with fewer output tiles than SMs stay with the library, which splits K
     if (epilogue == CUBLASLT_EPILOGUE_DEFAULT && use_tc_kernel(M, N, K, pad_c)) {
-        launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
+        if (!a_ready) launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
         launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
+        a_ready = b_ready = true;  // also for the library path below, should the kernel refuse
         if (b200gemm::tc_gemm_bf16(Ab, rowsA_p, lda_p, transA, Bb, rowsB_p, ldb_p, transB, C, N, M, N, Kp, alpha, stream)) return true;
     }
     const PlanKey key{M, N, K, transA ? 1 : 0, transB ? 1 : 0, (int)epilogue};
@@ -347,8 +390,8 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     if (!plan.has_algo) return false;
     if (epilogue != CUBLASLT_EPILOGUE_DEFAULT) cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias));
 
-    launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
-    launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
+    if (!a_ready) launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
+    if (!b_ready) launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
     const float beta = 0.0f;
     const cublasStatus_t st = cublasLtMatmul(g_own_lt, plan.op, &alpha, Bb, plan.a, Ab, plan.b, &beta, Cp, plan.c, Cp, plan.c,
                                              &plan.algo, workspace, kStagedWorkspace, stream);
@@ -365,6 +408,11 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
 }  // namespace
 
 extern "C" long long b200gemm_tc_launches(void) { return b200gemm::tc_gemm_launches(); }
+extern "C" long long b200gemm_staged_reuses(void) { return g_staged_reused; }
+extern "C" void b200gemm_forget_staged(void) {
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    for (KeptOperand& k : g_kept) k.src = nullptr;
+}
 
 extern "C" int b200gemm_check_device_fault(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -2;
