@@ -195,6 +195,8 @@ def run_gpt_step(args):
         env["B200GEMM_MATH"] = args.gemm
         # the reference model never rewrites a gradient between the dW and dX products that read it (src/model.cu:451-700)
         env.setdefault("B200GEMM_REUSE_STAGED", "1")
+        # ... and its LayerNorm outputs, LayerNorm / attention gradients are written by the drop-ins only: BF16 twins
+        env.setdefault("B200GEMM_TWINS", "1")
     res = subprocess.run([exe, "--steps", str(steps), "--warmup", str(min(args.warmup, 3))], env=env, capture_output=True, text=True)
     if res.returncode != 0:
         raise SystemExit(f"{name} failed on rank {rank}: {res.stderr[-2000:]}")
@@ -213,7 +215,7 @@ def run_gpt_step(args):
                                else f"GEMM drop-in, B200GEMM_MATH={args.gemm}",
                        "loss_adamw": "loss and AdamW drop-ins (libb200loss, optim/adamw_dropin.cu)" if name.endswith("_all")
                                      else "reference loss.cu and optimizer.cu"},
-            "loss_after_last_step": child["loss"],
+            "loss_after_last_step": child["loss"], "gemm_dropin": child.get("gemm_dropin"),
             "allreduce_ms_per_step": child.get("allreduce_ms_per_step"),
             "allreduce": "one in-place ncclAllReduce(avg) of the 163 M-float gradient buffer per step, timed with CUDA events on rank 0"}
     if world == 1 and args.impl != "reference" and not args.no_cpu_baseline:

@@ -72,6 +72,19 @@ def test_reusing_staged_gradients_does_not_change_the_step():
     env = {"B200ATTN_MATH": "bf16", "B200GEMM_MATH": "bf16", "B200GEMM_STAGE_MIN_MACS": "1"}
     ref = _run(_binary("gpt_step_dp_b200_all"), dict(env, B200GEMM_REUSE_STAGED="0"))
     got = _run(_binary("gpt_step_dp_b200_all"), dict(env, B200GEMM_REUSE_STAGED="1"))
+    assert got["gemm_dropin"]["staged_reuses"] > 0 and ref["gemm_dropin"]["staged_reuses"] == 0
+    assert abs(got["loss"] - ref["loss"]) <= 2e-3 * max(1.0, abs(ref["loss"])), (got["loss"], ref["loss"])
+
+
+def test_bf16_twins_do_not_change_the_step():
+    """B200GEMM_TWINS=1: the LayerNorm and attention-layout kernels write BF16 twins of the matrices the GEMMs read next
+    and the GEMM drop-in uses them instead of converting (twin_hits > 0); the loss after three steps is the one of the
+    run in which every operand is converted by the GEMM side."""
+    env = {"B200ATTN_MATH": "bf16", "B200GEMM_MATH": "bf16", "B200GEMM_STAGE_MIN_MACS": "1"}
+    ref = _run(_binary("gpt_step_dp_b200_all"), dict(env, B200GEMM_TWINS="0"))
+    got = _run(_binary("gpt_step_dp_b200_all"), dict(env, B200GEMM_TWINS="1"))
+    assert ref["gemm_dropin"]["linked"] and ref["gemm_dropin"]["twin_hits"] == 0
+    assert got["gemm_dropin"]["twin_hits"] > 0
     assert abs(got["loss"] - ref["loss"]) <= 2e-3 * max(1.0, abs(ref["loss"])), (got["loss"], ref["loss"])
 
 

@@ -13,6 +13,10 @@
 #include "../../include/b200attn.h"
 #include "kernels.cuh"
 
+// Defined by the GEMM drop-in (transformer-cuda_b200/gemm/matmul_dropin.cu) when it is linked into the same program;
+// NULL otherwise (a weak reference: this library does not depend on it).
+extern "C" void* b200gemm_bf16_twin(const void* fp32, int rows, int cols) __attribute__((weak));
+
 namespace {
 
 using namespace b200attn;
@@ -141,6 +145,14 @@ int device_state(cudaStream_t stream, DeviceState** out) {
 }
 
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// BF16 twin of an FP32 matrix that a GEMM of the caller reads next (the merged attention output feeds the output
+// projection, dqkv the QKV projection's backward): provided by the GEMM drop-in (libb200gemm) when that is linked into
+// the same program and B200GEMM_TWINS=1, else there is none and only the FP32 result is written.
+__nv_bfloat16* twin_for(const float* fp32, long long rows, long long cols) {
+    if (!b200gemm_bf16_twin || rows > 0x7fffffffLL || cols > 0x7fffffffLL) return nullptr;
+    return static_cast<__nv_bfloat16*>(b200gemm_bf16_twin(fp32, (int)rows, (int)cols));
+}
 
 // The BF16 copy registered for the FP32 tensor at `key` with exactly n elements, or NULL.
 __nv_bfloat16* find_shadow(DeviceState* st, const void* key, size_t n) {
@@ -491,7 +503,7 @@ extern "C" int b200attn_qkv_merge_grad_f32(const float* dq, const float* dk, con
     if (rc) return rc;
     if ((long long)B * T * H == 0) return B200ATTN_OK;
     REQUIRE_PTR(fn, dq); REQUIRE_PTR(fn, dk); REQUIRE_PTR(fn, dv); REQUIRE_PTR(fn, dqkv);
-    RETURN_IF_CUDA(launch_qkv_merge_grad<float>(dq, dk, dv, dqkv, B, T, H, d, (cudaStream_t)stream), fn);
+    RETURN_IF_CUDA(launch_qkv_merge_grad<float>(dq, dk, dv, dqkv, B, T, H, d, (cudaStream_t)stream, twin_for(dqkv, B * T, 3 * H * d)), fn);
     return B200ATTN_OK;
 }
 
@@ -649,7 +661,7 @@ extern "C" int b200attn_merge_heads_f32(const float* in, float* out, int B, int 
     if (rc) return rc;
     if ((long long)B * T * H == 0) return B200ATTN_OK;
     REQUIRE_PTR(fn, in); REQUIRE_PTR(fn, out);
-    RETURN_IF_CUDA(launch_merge_heads<float>(in, out, B, H, T, d, (cudaStream_t)stream), fn);
+    RETURN_IF_CUDA(launch_merge_heads<float>(in, out, B, H, T, d, (cudaStream_t)stream, twin_for(out, B * T, H * d)), fn);
     return B200ATTN_OK;
 }
 

@@ -36,9 +36,12 @@ cudaError_t launch_qkv_split(const float* qkv, TOut* q, TOut* k, TOut* v, int B,
                              cudaStream_t stream);
 template <typename TIn>
 cudaError_t launch_qkv_merge_grad(const TIn* dq, const TIn* dk, const TIn* dv, float* dqkv, int B, int T, int H, int d,
-                                  cudaStream_t stream);
+                                  cudaStream_t stream, __nv_bfloat16* twin = nullptr);
+// `twin` (both launchers): optional BF16 copy of the FP32 result written beside it, rows of round_up(row length, 8)
+// elements - the layout in which the GEMM drop-in keeps BF16 operands (see twin_for in api.cu).
 template <typename TIn>
-cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream);
+cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream,
+                               __nv_bfloat16* twin = nullptr);
 template <typename TOut>
 cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T, int d, cudaStream_t stream);
 // FP32 outputs plus BF16 copies in the same pass (d % 8 == 0, 16-byte aligned tensors: dual_layout_supported).

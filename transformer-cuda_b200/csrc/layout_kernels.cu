@@ -75,7 +75,11 @@ template <int VEC>
 __device__ __forceinline__ void store_from_f32(__nv_bfloat16* p, const float (&r)[VEC]) {
     if constexpr (VEC == 1) {
         *p = __float2bfloat16_rn(r[0]);
+    } else if constexpr (VEC == 4) {  // one 8-byte store (p is 8-byte aligned)
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+        *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     } else {
+        static_assert(VEC % 8 == 0, "BF16 stores move 1, 4 or a multiple of 8 elements");
 #pragma unroll
         for (int i = 0; i < VEC; i += 8) {
             uint32_t w[4];
@@ -168,7 +172,8 @@ __global__ void __launch_bounds__(kThreads) split_heads_dual_kernel(const float*
 template <typename TIn, int VEC>
 __global__ void __launch_bounds__(kThreads) qkv_merge_grad_kernel(const TIn* __restrict__ dq, const TIn* __restrict__ dk,
                                                                  const TIn* __restrict__ dv, float* __restrict__ dqkv,
-                                                                 int T, int H, int d, long long groups) {
+                                                                 int T, int H, int d, long long groups,
+                                                                 __nv_bfloat16* __restrict__ twin, int twin_ld) {
     long long g = blockIdx.x * (long long)kThreads + threadIdx.x;
     if (g >= groups) return;
     const int dvv = d / VEC;
@@ -181,13 +186,18 @@ __global__ void __launch_bounds__(kThreads) qkv_merge_grad_kernel(const TIn* __r
     const long long C = (long long)H * d;
     float* dst = dqkv + (b * T + t) * 3 * C + (long long)h * d + e;
     long long src = ((b * H + h) * T + t) * d + e;
+    // optional BF16 twin of dqkv (rows of twin_ld elements) for the GEMMs that read it next
+    __nv_bfloat16* tw = twin ? twin + (b * T + t) * twin_ld + (long long)h * d + e : nullptr;
     float a[VEC];
     load_as_f32<VEC>(dq + src, a);
     store_from_f32<VEC>(dst, a);
+    if (tw) store_from_f32<VEC>(tw, a);
     load_as_f32<VEC>(dk + src, a);
     store_from_f32<VEC>(dst + C, a);
+    if (tw) store_from_f32<VEC>(tw + C, a);
     load_as_f32<VEC>(dv + src, a);
     store_from_f32<VEC>(dst + 2 * C, a);
+    if (tw) store_from_f32<VEC>(tw + 2 * C, a);
 }
 
 // (B,H,T,d) <-> (B,T,H*d); TO_MERGED selects the direction. Thread order follows (B,T,H*d).
@@ -196,7 +206,8 @@ __global__ void __launch_bounds__(kThreads) head_transpose_kernel(const THead* _
                                                                  THead* __restrict__ head_out,
                                                                  const float* __restrict__ merged_in,
                                                                  float* __restrict__ merged_out, int T, int H, int d,
-                                                                 long long groups) {
+                                                                 long long groups, __nv_bfloat16* __restrict__ twin = nullptr,
+                                                                 int twin_ld = 0) {
     long long g = blockIdx.x * (long long)kThreads + threadIdx.x;
     if (g >= groups) return;
     const int dv = d / VEC;
@@ -212,6 +223,7 @@ __global__ void __launch_bounds__(kThreads) head_transpose_kernel(const THead* _
     if constexpr (TO_MERGED) {
         load_as_f32<VEC>(head_in + head, a);
         store_from_f32<VEC>(merged_out + merged, a);
+        if (twin) store_from_f32<VEC>(twin + (b * T + t) * twin_ld + (long long)h * d + e, a);  // BF16 twin of the merged rows
     } else {
         load_as_f32<VEC>(merged_in + merged, a);
         store_from_f32<VEC>(head_out + head, a);
@@ -291,40 +303,43 @@ template cudaError_t launch_qkv_split<__nv_bfloat16>(const float*, __nv_bfloat16
 
 template <typename TIn>
 cudaError_t launch_qkv_merge_grad(const TIn* dq, const TIn* dk, const TIn* dv, float* dqkv, int B, int T, int H, int d,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, __nv_bfloat16* twin) {
     constexpr int VEC = sizeof(TIn) == 2 ? 8 : 4;
     long long n = (long long)B * T * H * d;
     if (n == 0) return cudaSuccess;
     bool vec_ok = (d % VEC == 0) && aligned16(dqkv) && aligned16(dq) && aligned16(dk) && aligned16(dv);
+    const int twin_ld = (3 * H * d + 7) / 8 * 8;  // the layout the GEMM side expects: leading dimension rounded up to 8
     if (vec_ok) {
         long long groups = n / VEC;
-        qkv_merge_grad_kernel<TIn, VEC><<<blocks_for(groups), kThreads, 0, stream>>>(dq, dk, dv, dqkv, T, H, d, groups);
+        qkv_merge_grad_kernel<TIn, VEC><<<blocks_for(groups), kThreads, 0, stream>>>(dq, dk, dv, dqkv, T, H, d, groups, twin, twin_ld);
     } else {
-        qkv_merge_grad_kernel<TIn, 1><<<blocks_for(n), kThreads, 0, stream>>>(dq, dk, dv, dqkv, T, H, d, n);
+        qkv_merge_grad_kernel<TIn, 1><<<blocks_for(n), kThreads, 0, stream>>>(dq, dk, dv, dqkv, T, H, d, n, twin, twin_ld);
     }
     return cudaGetLastError();
 }
 template cudaError_t launch_qkv_merge_grad<float>(const float*, const float*, const float*, float*, int, int, int, int,
-                                                 cudaStream_t);
+                                                 cudaStream_t, __nv_bfloat16*);
 template cudaError_t launch_qkv_merge_grad<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*,
-                                                         const __nv_bfloat16*, float*, int, int, int, int, cudaStream_t);
+                                                         const __nv_bfloat16*, float*, int, int, int, int, cudaStream_t,
+                                                         __nv_bfloat16*);
 
 template <typename TIn>
-cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream) {
+cudaError_t launch_merge_heads(const TIn* in, float* out, int B, int H, int T, int d, cudaStream_t stream, __nv_bfloat16* twin) {
     constexpr int VEC = sizeof(TIn) == 2 ? 8 : 4;
     long long n = (long long)B * T * H * d;
     if (n == 0) return cudaSuccess;
     bool vec_ok = (d % VEC == 0) && aligned16(in) && aligned16(out);
+    const int twin_ld = (H * d + 7) / 8 * 8;
     if (vec_ok) {
         long long groups = n / VEC;
-        head_transpose_kernel<TIn, VEC, true><<<blocks_for(groups), kThreads, 0, stream>>>(in, nullptr, nullptr, out, T, H, d, groups);
+        head_transpose_kernel<TIn, VEC, true><<<blocks_for(groups), kThreads, 0, stream>>>(in, nullptr, nullptr, out, T, H, d, groups, twin, twin_ld);
     } else {
-        head_transpose_kernel<TIn, 1, true><<<blocks_for(n), kThreads, 0, stream>>>(in, nullptr, nullptr, out, T, H, d, n);
+        head_transpose_kernel<TIn, 1, true><<<blocks_for(n), kThreads, 0, stream>>>(in, nullptr, nullptr, out, T, H, d, n, twin, twin_ld);
     }
     return cudaGetLastError();
 }
-template cudaError_t launch_merge_heads<float>(const float*, float*, int, int, int, int, cudaStream_t);
-template cudaError_t launch_merge_heads<__nv_bfloat16>(const __nv_bfloat16*, float*, int, int, int, int, cudaStream_t);
+template cudaError_t launch_merge_heads<float>(const float*, float*, int, int, int, int, cudaStream_t, __nv_bfloat16*);
+template cudaError_t launch_merge_heads<__nv_bfloat16>(const __nv_bfloat16*, float*, int, int, int, int, cudaStream_t, __nv_bfloat16*);
 
 template <typename TOut>
 cudaError_t launch_split_heads(const float* dout, TOut* din, int B, int H, int T, int d, cudaStream_t stream) {

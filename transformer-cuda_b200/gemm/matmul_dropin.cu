@@ -313,6 +313,34 @@ struct KeptOperand {
 KeptOperand g_kept[2];
 long long g_staged_calls = 0, g_staged_reused = 0;
 
+// BF16 twins. A kernel that is the only writer of an FP32 matrix the GEMMs read (a LayerNorm output, a gradient coming out
+// of a LayerNorm or attention backward) can ask for a BF16 twin of it - b200gemm_bf16_twin(), below - and write the BF16
+// values beside the FP32 ones; a staged product that reads a matrix with a twin (same address, same shape) uses the twin
+// and converts nothing. Twins are allocated here on first request in the staged layout (leading dimension and row count
+// rounded up to 8, padding zeroed once) and live until b200gemm_release_twins(). Off unless B200GEMM_TWINS=1: the
+// arrangement is only sound while nothing else writes those FP32 matrices.
+struct Twin {
+    void* bf16 = nullptr;
+    int rows = 0, cols = 0;
+};
+std::unordered_map<const void*, Twin> g_twins;
+long long g_twin_hits = 0;
+bool twins_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("B200GEMM_TWINS");
+        return e && !strcmp(e, "1") && math_mode() == Math::kBf16;
+    }();
+    return v;
+}
+// caller holds g_plans_mutex
+void* find_twin(const void* fp32, int rows, int cols) {
+    if (!twins_enabled()) return nullptr;
+    auto it = g_twins.find(fp32);
+    if (it == g_twins.end() || it->second.rows != rows || it->second.cols != cols) return nullptr;
+    ++g_twin_hits;
+    return it->second.bf16;
+}
+
 // Returns false when the staged path could not run (the caller then takes the direct path).
 bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, int K, bool transA, bool transB, float alpha,
                       cudaStream_t stream, cublasLtEpilogue_t epilogue = CUBLASLT_EPILOGUE_DEFAULT, const float* bias = nullptr) {
@@ -338,14 +366,18 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     float* Cp = pad_c ? reinterpret_cast<float*>(base + kStagedWorkspace + bytesA + bytesB) : C;
     bool a_ready = false, b_ready = false;
     const long long call = g_staged_calls++;
+    if (void* t = find_twin(A, rowsA, colsA)) Ab = static_cast<__nv_bfloat16*>(t), a_ready = true;
+    if (void* t = find_twin(B, rowsB, colsB)) Bb = static_cast<__nv_bfloat16*>(t), b_ready = true;
     if (reuse_staged()) {
         int a_slot = -1;
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < 2 && !a_ready; ++i)
             if (g_kept[i].src == A && g_kept[i].rows == rowsA && g_kept[i].cols == colsA && g_kept[i].call == call - 1) a_slot = i;
         if (a_slot >= 0) Ab = static_cast<__nv_bfloat16*>(g_kept[a_slot].buf.p), a_ready = true, ++g_staged_reused;
         KeptOperand& keep = g_kept[a_slot >= 0 ? 1 - a_slot : int(call & 1)];
-        keep.src = nullptr;
-        if (void* kb = keep.buf.get(bytesB)) Bb = static_cast<__nv_bfloat16*>(kb), keep.src = B, keep.rows = rowsB, keep.cols = colsB, keep.call = call;
+        if (!b_ready) {  // (a B with a twin needs no keeping: the next call finds the same twin for its A)
+            keep.src = nullptr;
+            if (void* kb = keep.buf.get(bytesB)) Bb = static_cast<__nv_bfloat16*>(kb), keep.src = B, keep.rows = rowsB, keep.cols = colsB, keep.call = call;
+        }
     }
 
     const bool pad_any = pad_c || Kp != K;
@@ -354,7 +386,7 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
     // padded result tile, no copy back); products with fewer output tiles than SMs stay with the library, which splits K
     if (epilogue == CUBLASLT_EPILOGUE_DEFAULT && use_tc_kernel(M, N, K, pad_c)) {
         if (!a_ready) launch_stage_bf16(A, Ab, rowsA, colsA, colsA, rowsA_p, lda_p, stream);
-        launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
+        if (!b_ready) launch_stage_bf16(B, Bb, rowsB, colsB, colsB, rowsB_p, ldb_p, stream);
         a_ready = b_ready = true;  // also for the library path below, should the kernel refuse
         if (b200gemm::tc_gemm_bf16(Ab, rowsA_p, lda_p, transA, Bb, rowsB_p, ldb_p, transB, C, N, M, N, Kp, alpha, stream)) return true;
     }
@@ -409,6 +441,31 @@ bool staged_bf16_gemm(const float* A, const float* B, float* C, int M, int N, in
 
 extern "C" long long b200gemm_tc_launches(void) { return b200gemm::tc_gemm_launches(); }
 extern "C" long long b200gemm_staged_reuses(void) { return g_staged_reused; }
+extern "C" void* b200gemm_bf16_twin(const void* fp32, int rows, int cols) {
+    if (!fp32 || rows <= 0 || cols <= 0) return nullptr;
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    if (!twins_enabled()) return nullptr;
+    Twin& t = g_twins[fp32];
+    if (t.bf16 && t.rows == rows && t.cols == cols) return t.bf16;
+    if (t.bf16) cudaFree(t.bf16);
+    t = Twin{};
+    const size_t bytes = size_t(round_up_int(rows, 8)) * round_up_int(cols, 8) * 2;
+    if (cudaMalloc(&t.bf16, bytes) != cudaSuccess || cudaMemset(t.bf16, 0, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        if (t.bf16) cudaFree(t.bf16);
+        g_twins.erase(fp32);
+        return nullptr;
+    }
+    t.rows = rows, t.cols = cols;
+    return t.bf16;
+}
+extern "C" long long b200gemm_twin_hits(void) { return g_twin_hits; }
+extern "C" void b200gemm_release_twins(void) {
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    cudaDeviceSynchronize();
+    for (auto& kv : g_twins) cudaFree(kv.second.bf16);
+    g_twins.clear();
+}
 extern "C" void b200gemm_forget_staged(void) {
     std::lock_guard<std::mutex> lock(g_plans_mutex);
     for (KeptOperand& k : g_kept) k.src = nullptr;

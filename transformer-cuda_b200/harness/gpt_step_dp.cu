@@ -52,6 +52,11 @@ static int env_int(const char* name, int dflt) {
     return s ? atoi(s) : dflt;
 }
 
+// Counters of the GEMM drop-in, present when libb200gemm is linked in (weak: the other builds have none).
+extern "C" long long b200gemm_tc_launches(void) __attribute__((weak));
+extern "C" long long b200gemm_staged_reuses(void) __attribute__((weak));
+extern "C" long long b200gemm_twin_hits(void) __attribute__((weak));
+
 int main(int argc, char** argv) {
     int steps = 5, warmup = 2;
     TransformerConfig cfg;
@@ -198,9 +203,12 @@ int main(int argc, char** argv) {
         printf("{\"metric\": \"gpt_step_tokens_per_s\", \"value\": %.1f, \"unit\": \"tokens/s\", \"n_gpus\": %d, \"steps\": %d, "
                "\"warmup\": %d, \"ms_per_step\": %.3f, \"allreduce_ms_per_step\": %.3f, \"loss\": %.5f, \"attention\": \"%s\", \"params\": %zu, "
                "\"config\": {\"L\": %zu, \"C\": %zu, \"H\": %zu, \"d_ff\": %zu, \"V\": %zu, \"T\": %d, \"per_gpu_batch\": %d, "
-               "\"optimizer\": \"AdamW lr=3e-4 betas=(0.9,0.95) wd=0.1 clip=1.0\", \"parallelism\": \"dp%d, one ncclAllReduce(avg) of the gradient buffer per step\"}}\n",
+               "\"optimizer\": \"AdamW lr=3e-4 betas=(0.9,0.95) wd=0.1 clip=1.0\", \"parallelism\": \"dp%d, one ncclAllReduce(avg) of the gradient buffer per step\"}, "
+               "\"gemm_dropin\": {\"linked\": %s, \"tcgen05_launches\": %lld, \"staged_reuses\": %lld, \"twin_hits\": %lld}}\n",
                (double)world * B * T / (ms_step * 1e-3), world, steps, warmup, ms_step, ar_ms / steps, host_loss, attn, n_params,
-               cfg.num_layers, cfg.d_model, cfg.num_heads, cfg.d_ff, cfg.vocab_size, T, B, world);
+               cfg.num_layers, cfg.d_model, cfg.num_heads, cfg.d_ff, cfg.vocab_size, T, B, world,
+               b200gemm_tc_launches ? "true" : "false", b200gemm_tc_launches ? b200gemm_tc_launches() : 0LL,
+               b200gemm_staged_reuses ? b200gemm_staged_reuses() : 0LL, b200gemm_twin_hits ? b200gemm_twin_hits() : 0LL);
     }
     if (comm) ncclCommDestroy(comm);
     return 0;

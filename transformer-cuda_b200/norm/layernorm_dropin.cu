@@ -17,10 +17,26 @@
 //     shared-memory atomics.
 #include "kernels/layernorm.cuh"
 
+#include <cuda_bf16.h>
+
 #include <cstdint>
 #include <cstdio>
 
+// Defined by the GEMM drop-in (libb200gemm.a) when it is linked into the same program, else NULL: a BF16 twin of an FP32
+// matrix the GEMMs will read, written here beside the FP32 values so that the GEMM side converts nothing (B200GEMM_TWINS=1).
+extern "C" void* b200gemm_bf16_twin(const void* fp32, int rows, int cols) __attribute__((weak));
+
 namespace {
+
+__device__ __forceinline__ void store_twin4(__nv_bfloat16* twin_row, int i, const float4& r) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+    uint2 w;
+    w.x = *reinterpret_cast<const unsigned int*>(&lo), w.y = *reinterpret_cast<const unsigned int*>(&hi);
+    reinterpret_cast<uint2*>(twin_row)[i] = w;
+}
+__nv_bfloat16* twin_of(const float* fp32, int rows, int cols) {
+    return b200gemm_bf16_twin ? static_cast<__nv_bfloat16*>(b200gemm_bf16_twin(fp32, rows, cols)) : nullptr;
+}
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
@@ -39,7 +55,7 @@ template <int kVec>
 __global__ void __launch_bounds__(kThreads) ln_forward_reg_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
                                                                    const float* __restrict__ beta, float* __restrict__ out,
                                                                    float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                                                                   int N, float eps) {
+                                                                   int N, float eps, __nv_bfloat16* __restrict__ twin) {
     constexpr int C = 128 * kVec;
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
@@ -73,6 +89,7 @@ __global__ void __launch_bounds__(kThreads) ln_forward_reg_kernel(const float* _
         r.z = ((v[j].z - mean) * rstd) * g.z + b.z;
         r.w = ((v[j].w - mean) * rstd) * g.w + b.w;
         orow[i] = r;
+        if (twin) store_twin4(twin + (size_t)row * C, i, r);
     }
 }
 
@@ -121,7 +138,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     ln_backward_reg_kernel(const float* __restrict__ dout, const float* __restrict__ x, const float* __restrict__ gamma,
                            const float* __restrict__ mean_in, const float* __restrict__ rstd_in, float* __restrict__ dx,
                            float* __restrict__ dgamma, float* __restrict__ dbeta, int N, const float* __restrict__ residual,
-                           int accumulate) {
+                           int accumulate, __nv_bfloat16* __restrict__ twin) {
     constexpr int C = 128 * kVec;
     extern __shared__ __align__(16) float smem[];  // kWarps * C floats
     const int lane = threadIdx.x & 31;
@@ -169,6 +186,7 @@ __global__ void __launch_bounds__(kThreads, 2)
                 r.x += o.x, r.y += o.y, r.z += o.z, r.w += o.w;
             }
             dxr[i] = r;
+            if (twin) store_twin4(twin + (size_t)row * C, i, r);
         }
     }
     if (dgamma) flush_column_sums<kVec>(dg, smem, dgamma);
@@ -244,7 +262,7 @@ void launch_backward_reg(const float* dout, const float* x, const float* gamma, 
     }
     const int ctas_needed = (N + kWarps - 1) / kWarps, persistent = 2 * sm_count();
     ln_backward_reg_kernel<kVec><<<ctas_needed < persistent ? ctas_needed : persistent, kThreads, smem, stream>>>(
-        dout, x, gamma, mean, rstd, dx, dgamma, dbeta, N, residual, accumulate ? 1 : 0);
+        dout, x, gamma, mean, rstd, dx, dgamma, dbeta, N, residual, accumulate ? 1 : 0, twin_of(dx, N, 128 * kVec));
 }
 
 }  // namespace
@@ -254,8 +272,9 @@ void layernorm_forward(const float* x, const float* gamma, const float* beta, fl
     if (N <= 0 || C <= 0) return;
     const int grid = (N + kWarps - 1) / kWarps;
     const bool reg = C % 128 == 0 && C <= 128 * kMaxVec && aligned16({x, gamma, beta, out});
+    __nv_bfloat16* twin = reg ? twin_of(out, N, C) : nullptr;  // (the generic kernels write no twin: the GEMMs convert)
 #define B200NORM_FWD(K) \
-    case K: ln_forward_reg_kernel<K><<<grid, kThreads, 0, stream>>>(x, gamma, beta, out, mean, rstd, N, eps); break;
+    case K: ln_forward_reg_kernel<K><<<grid, kThreads, 0, stream>>>(x, gamma, beta, out, mean, rstd, N, eps, twin); break;
     if (reg) {
         switch (C / 128) {
             B200NORM_FWD(1) B200NORM_FWD(2) B200NORM_FWD(3) B200NORM_FWD(4) B200NORM_FWD(5) B200NORM_FWD(6) B200NORM_FWD(7)
