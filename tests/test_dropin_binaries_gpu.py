@@ -146,8 +146,9 @@ def test_staged_operand_reuse_between_the_backward_pair():
 @pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])
 def test_loss_dropin_meets_the_reference_gate_in_fp32(tmp_path, case):
     """oracle/_ref/parity_audit_all: the reference model with its attention kernels, its GEMM wrappers, its loss
-    launcher (src/kernels/loss.cu) AND its LayerNorm launchers (src/kernels/layernorm.cu) replaced - libb200loss and
-    libb200norm behind the unchanged declarations of include/kernels/loss.cuh and layernorm.cuh. Loss, logits and
+    launcher (src/kernels/loss.cu), its LayerNorm launchers (src/kernels/layernorm.cu) AND its GELU launchers
+    (src/kernels/ffn.cu) replaced - libb200loss, libb200norm and libb200ffn behind the unchanged declarations of
+    include/kernels/loss.cuh, layernorm.cuh and ffn.cuh. Loss, logits and
     every gradient (all of which flow from d_logits, through five LayerNorms) still meet the gates of
     scripts/compare_parity.py:108-117."""
     exe = _binary("parity_audit_all")
@@ -156,7 +157,7 @@ def test_loss_dropin_meets_the_reference_gate_in_fp32(tmp_path, case):
     env = dict(os.environ, B200ATTN_MATH="fp32", B200GEMM_MATH="fp32")
     res = subprocess.run([exe, str(work), "--tiled_attn"], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout + res.stderr
-    for tag in ("[b200attn]", "b200gemm:", "[b200loss]", "[b200norm]"):
+    for tag in ("[b200attn]", "b200gemm:", "[b200loss]", "[b200norm]", "[b200ffn]"):
         assert tag not in res.stderr
     load = lambda n: np.fromfile(os.path.join(work, n), dtype=np.float32)
     assert _max_abs(load("cuda_logits.bin"), load("pytorch_logits.bin")) <= 1e-5
@@ -178,8 +179,9 @@ def test_adamw_dropin_against_host_restatement():
 
 
 def test_reference_kernel_test_suite_with_the_layernorm_dropin():
-    """tests/test_kernels.cu of the reference, unchanged, with src/kernels/layernorm.cu replaced by libb200norm as well
-    as attention.cu by libb200attn: its LayerNorm test (:13-89) and every other test pass."""
+    """tests/test_kernels.cu of the reference, unchanged, with src/kernels/layernorm.cu replaced by libb200norm and
+    src/kernels/ffn.cu by libb200ffn as well as attention.cu by libb200attn: its LayerNorm test (:13-89), its GELU test
+    and every other test pass."""
     res = subprocess.run([_binary("test_kernels_all")], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "All isolated kernel tests passed" in res.stdout

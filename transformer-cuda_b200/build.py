@@ -2,7 +2,7 @@
 and lib/libb200attn.a (the same objects, for static linking in place of the reference's
 src/kernels/attention.cu); beside them the drop-ins for the callers of the path: lib/libb200gemm.a
 (src/kernels/matmul.cu), lib/libb200loss.so / .a (src/kernels/loss.cu) and lib/libb200norm.a
-(src/kernels/layernorm.cu). Rebuilds only when a source is newer than the library."""
+(src/kernels/layernorm.cu), lib/libb200ffn.a (src/kernels/ffn.cu). Rebuilds only when a source is newer than the library."""
 import os
 import shutil
 import subprocess
@@ -20,6 +20,7 @@ SO = os.path.join(LIBDIR, "libb200attn.so")
 AR = os.path.join(LIBDIR, "libb200attn.a")
 GEMM_AR = os.path.join(LIBDIR, "libb200gemm.a")
 NORM_AR = os.path.join(LIBDIR, "libb200norm.a")
+FFN_AR = os.path.join(LIBDIR, "libb200ffn.a")
 LOSS_SO = os.path.join(LIBDIR, "libb200loss.so")
 LOSS_AR = os.path.join(LIBDIR, "libb200loss.a")
 
@@ -107,6 +108,15 @@ def build(verbose=False, force=False, ptxas_info=False):
         if os.path.exists(NORM_AR):
             os.remove(NORM_AR)
         subprocess.check_call(["ar", "rcs", NORM_AR, norm_obj])
+    # the GELU drop-in
+    ffn_src = os.path.join(HERE, "ffn", "gelu_dropin.cu")
+    ffn_obj = os.path.join(OBJDIR, "gelu_dropin.o")
+    if force or _stale(ffn_obj, [ffn_src, os.path.join(HERE, "..", "include", "kernels", "ffn.cuh")]):
+        subprocess.check_call([nvcc] + ARCH + FLAGS + ["--use_fast_math", "-I", os.path.join(HERE, "..", "include"), "-c", ffn_src, "-o", ffn_obj])
+    if force or _stale(FFN_AR, [ffn_obj]):
+        if os.path.exists(FFN_AR):
+            os.remove(FFN_AR)
+        subprocess.check_call(["ar", "rcs", FFN_AR, ffn_obj])
     return SO
 
 

@@ -321,7 +321,8 @@ long long g_staged_calls = 0, g_staged_reused = 0;
 // arrangement is only sound while nothing else writes those FP32 matrices.
 struct Twin {
     void* bf16 = nullptr;
-    int rows = 0, cols = 0;
+    int rows = 0, cols = 0;   // rows = -1: a flat twin of `count` elements (its producer knows no row structure)
+    long long count = 0;
 };
 std::unordered_map<const void*, Twin> g_twins;
 long long g_twin_hits = 0;
@@ -336,9 +337,14 @@ bool twins_enabled() {
 void* find_twin(const void* fp32, int rows, int cols) {
     if (!twins_enabled()) return nullptr;
     auto it = g_twins.find(fp32);
-    if (it == g_twins.end() || it->second.rows != rows || it->second.cols != cols) return nullptr;
+    if (it == g_twins.end()) return nullptr;
+    const Twin& t = it->second;
+    // a flat twin is the staged layout of any rows x cols view with nothing to pad
+    const bool match = t.rows >= 0 ? (t.rows == rows && t.cols == cols)
+                                   : (t.count == (long long)rows * cols && rows % 8 == 0 && cols % 8 == 0);
+    if (!match) return nullptr;
     ++g_twin_hits;
-    return it->second.bf16;
+    return t.bf16;
 }
 
 // Returns false when the staged path could not run (the caller then takes the direct path).
@@ -457,6 +463,22 @@ extern "C" void* b200gemm_bf16_twin(const void* fp32, int rows, int cols) {
         return nullptr;
     }
     t.rows = rows, t.cols = cols;
+    return t.bf16;
+}
+extern "C" void* b200gemm_bf16_twin_flat(const void* fp32, long long count) {
+    if (!fp32 || count <= 0) return nullptr;
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    if (!twins_enabled()) return nullptr;
+    Twin& t = g_twins[fp32];
+    if (t.bf16 && t.rows < 0 && t.count == count) return t.bf16;
+    if (t.bf16) cudaFree(t.bf16);
+    t = Twin{};
+    if (cudaMalloc(&t.bf16, size_t(count) * 2) != cudaSuccess) {
+        cudaGetLastError();
+        g_twins.erase(fp32);
+        return nullptr;
+    }
+    t.rows = -1, t.count = count;
     return t.bf16;
 }
 extern "C" long long b200gemm_twin_hits(void) { return g_twin_hits; }
