@@ -3,13 +3,17 @@
 // M x K or K x M, B stored K x N or N x K, leading dimensions multiples of 8). Used by the staged path of the GEMM drop-in
 // in place of the library call when B200GEMM_KERNEL=tcgen05.
 //
-//   * One persistent CTA per SM walks 128 x 256 output tiles (M fastest, so the CTAs running together share one
+//   * One persistent CTA per SM walks 256 x 256 output tiles (M fastest, so the CTAs running together share one
 //     256-column panel of B in L2). 192 threads in three roles: warp 4 issues TMA loads (cp.async.bulk.tensor, 128-byte
-//     swizzle, no multicast) into a four-stage ring of 48 KB (A 128 x 64, B 256 x 64); one thread of warp 5 issues
-//     tcgen05.mma (M = 128, N = 256, K = 16, both operands from shared memory: 12 KB per 128 cycles, under the 128 B/clk
-//     of the port, so one CTA per SM reaches the full MMA rate without pairing); warps 0-3 are the epilogue.
-//   * The FP32 accumulator (128 lanes x 256 columns) lives in TMEM twice (512 columns): the MMAs of tile i+1 run into
-//     one buffer while the epilogue warps drain tile i from the other.
+//     swizzle, no multicast) into a three-stage ring of 64 KB (A 256 x 64, B 256 x 64); one thread of warp 5 issues
+//     tcgen05.mma (M = 128, N = 256, K = 16; two per K step, one for each half of the tile's rows, both reading the same
+//     B tile); warps 0-3 are the epilogue.
+//   * Why 256 x 256: what paces a one-CTA GEMM on this part is the L2 -> SM path, not the tensor pipe. With 128 x 256
+//     tiles (and a double-buffered accumulator) this kernel moved 48 KB per 512 cycles of MMA and ran at 41 % of the MMA
+//     rate with 9.8 TB/s of L2 reads (measured on the K = 50257 product of the head: about 38 B/clk per SM); a 256 x 256
+//     tile needs 64 KB per 1024 cycles, a third less per FLOP. The price is TMEM: two 128 x 256 FP32 accumulators fill
+//     all 512 columns, so the epilogue of a tile does not overlap the MMAs of the next (its loads do: the producer runs
+//     ahead into the ring).
 //   * Transposed operands cost nothing: an operand whose M / N index is the contiguous one is loaded as 64 x 64 boxes and
 //     described to the MMA as MN-major (descriptor LBO = distance between 64-wide atoms, K step = 16 rows = 2 KB); a
 //     K-contiguous operand is one box and K-major (K step = 32 bytes inside the swizzle atom).
@@ -33,9 +37,9 @@ namespace {
 
 using namespace b200attn;
 
-constexpr int kBM = 128, kBN = 256, kBK = 64;
-constexpr int kStages = 4;
-constexpr int kABytes = kBM * kBK * 2;      // 16 KB
+constexpr int kBM = 256, kBN = 256, kBK = 64;
+constexpr int kStages = 3;
+constexpr int kABytes = kBM * kBK * 2;      // 32 KB
 constexpr int kBBytes = kBN * kBK * 2;      // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAtom64Bytes = 64 * 128;      // a 64-row x 64-element box: 8 KB
@@ -61,13 +65,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     float* epi = reinterpret_cast<float*>(ring + kStages * kStageBytes);
-    __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+    __shared__ uint64_t full[kStages], empty[kStages], acc_full, acc_empty;
     __shared__ uint32_t tmem_base_sh, abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], 1);
-        for (int b = 0; b < 2; ++b) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], kEpiWarps * 32);
+        mbar_init(&acc_full, 1), mbar_init(&acc_empty, kEpiWarps * 32);
         abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&a.map_a);
@@ -97,10 +101,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     mbar_expect_tx(&full[s], kStageBytes);
                     uint8_t* sA = ring + s * kStageBytes;
                     uint8_t* sB = sA + kABytes;
-                    if (A_MN) {  // stored K x M: two boxes of 64 (M) x 64 (K rows)
-                        tma_load_2d(sA, &a.map_a, &full[s], m0, k0);
-                        tma_load_2d(sA + kAtom64Bytes, &a.map_a, &full[s], m0 + 64, k0);
-                    } else {     // stored M x K: one box of 64 (K) x 128 (M rows)
+                    if (A_MN) {  // stored K x M: four boxes of 64 (M) x 64 (K rows)
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) tma_load_2d(sA + q * kAtom64Bytes, &a.map_a, &full[s], m0 + 64 * q, k0);
+                    } else {     // stored M x K: one box of 64 (K) x 256 (M rows)
                         tma_load_2d(sA, &a.map_a, &full[s], k0, m0);
                     }
                     if (B_MN) {  // stored K x N: four boxes of 64 (N) x 64 (K rows)
@@ -114,11 +118,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
         __syncwarp();
     } else if (warp == kMmaWarp) {
-        constexpr uint32_t idesc = make_idesc_bf16(kBM, kBN, A_MN, B_MN);
+        constexpr uint32_t idesc = make_idesc_bf16(128, kBN, A_MN, B_MN);
+        // rows [128, 256) of the A tile: 128 rows of 128 bytes further on (K-major), or two 64-wide atoms further (MN-major)
+        constexpr uint32_t a_hi = A_MN ? 2 * kAtom64Bytes : 128 * 128;
         int g = 0, lt = 0;
         for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
-            const int buf = lt & 1;
-            if (lt >= 2) mbar_wait(&acc_empty[buf], ((lt >> 1) - 1) & 1, &abort_flag, fault, 0x61);
+            if (lt >= 1) mbar_wait(&acc_empty, (lt - 1) & 1, &abort_flag, fault, 0x61);
             tc_fence_after();
             for (int kb = 0; kb < k_blocks; ++kb, ++g) {
                 const int s = g % kStages;
@@ -129,32 +134,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     const uint64_t a_desc = make_smem_desc_sw128(sA, A_MN ? kAtom64Bytes : 0, 1024);
                     const uint64_t b_desc = make_smem_desc_sw128(sB, B_MN ? kAtom64Bytes : 0, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; ++kk)
-                        tc_mma_ss(tmem + buf * kBN, desc_advance(a_desc, A_MN ? kk * 2048 : kk * 32),
-                                  desc_advance(b_desc, B_MN ? kk * 2048 : kk * 32), idesc, (kb > 0) || (kk > 0));
+                    for (int kk = 0; kk < kBK / 16; ++kk) {
+                        const uint64_t ad = desc_advance(a_desc, A_MN ? kk * 2048 : kk * 32);
+                        const uint64_t bd = desc_advance(b_desc, B_MN ? kk * 2048 : kk * 32);
+                        tc_mma_ss(tmem, ad, bd, idesc, (kb > 0) || (kk > 0));
+                        tc_mma_ss(tmem + kBN, desc_advance(ad, a_hi), bd, idesc, (kb > 0) || (kk > 0));
+                    }
                     tc_commit(&empty[s]);
-                    if (kb == k_blocks - 1) tc_commit(&acc_full[buf]);
+                    if (kb == k_blocks - 1) tc_commit(&acc_full);
                 }
                 __syncwarp();
             }
         }
     } else {
-        // epilogue: warp w owns TMEM lanes [32w, 32w + 32) = rows m0 + 32w ... of the tile
+        // epilogue: warp w owns TMEM lanes [32w, 32w + 32) = rows 32w ... of either half of the tile
         float* stage = epi + warp * 32 * kEpiPitch;
         int lt = 0;
         for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
-            const int buf = lt & 1;
-            const int m0 = (t % m_tiles) * kBM + warp * 32, n0 = (t / m_tiles) * kBN;
-            mbar_wait(&acc_full[buf], (lt >> 1) & 1, &abort_flag, fault, 0x63);
+            const int n0 = (t / m_tiles) * kBN;
+            mbar_wait(&acc_full, lt & 1, &abort_flag, fault, 0x63);
             tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
+            for (int c = 0; c < 2 * (kBN / 32); ++c) {
+                const int half = c / (kBN / 32), cc = c % (kBN / 32);  // accumulator (row half), 32-column chunk
+                const int m0 = (t % m_tiles) * kBM + half * 128 + warp * 32;
                 uint32_t v[32];
-                tmem_ld32(tmem_addr(tmem, warp * 32, buf * kBN + c * 32), v);
+                tmem_ld32(tmem_addr(tmem, warp * 32, half * kBN + cc * 32), v);
                 tmem_wait_ld();
-                if (c == kBN / 32 - 1) {  // the accumulator has been read completely: hand it back to the MMA warp
+                if (c == 2 * (kBN / 32) - 1) {  // both accumulators have been read completely: hand them back to the MMA warp
                     tc_fence_before();
-                    mbar_arrive(&acc_empty[buf]);
+                    mbar_arrive(&acc_empty);
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
@@ -165,7 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 float o[32];
 #pragma unroll
                 for (int r = 0; r < 32; ++r) o[r] = stage[r * kEpiPitch + lane];
-                const int col = n0 + c * 32 + lane;
+                const int col = n0 + cc * 32 + lane;
                 const int rows = col < a.N ? a.M - m0 : 0;  // rows of this warp's strip that exist (may exceed 32)
                 float* dst = a.C + (long long)m0 * a.ldc + col;
 #pragma unroll

@@ -13,7 +13,7 @@ namespace b200gemm {
 bool tc_gemm_bf16(const void* A, int rows_a, int lda, bool trans_a, const void* B, int rows_b, int ldb, bool trans_b, float* C,
                   long long ldc, int M, int N, int K, float alpha, cudaStream_t stream);
 
-// Number of 128 x 256 output tiles of an M x N product (the kernel runs one persistent CTA per SM over them).
+// Number of 256 x 256 output tiles of an M x N product (the kernel runs one persistent CTA per SM over them).
 int tc_gemm_tiles(int M, int N);
 
 // Launches of the kernel by this process so far.

@@ -252,7 +252,7 @@ bool stage_all() {
 //   B200GEMM_KERNEL=auto (default)  those it wins: a result with an unaligned leading dimension that is larger than the
 //                                   operands (the language-model-head forward: 3.3 GB of logits written in place instead
 //                                   of into a padded tile and copied; measured 1.73 against 2.20 ms)
-//   B200GEMM_KERNEL=tcgen05         every staged product with at least 120 output tiles and no epilogue
+//   B200GEMM_KERNEL=tcgen05         every staged product with at least 74 output tiles (256 x 256) and no epilogue
 //   B200GEMM_KERNEL=library         none
 // Elsewhere the library's two-CTA kernels are faster: a one-CTA kernel with both operands in shared memory moves 96 KB
 // through the 128 B/clk port per 512 cycles of MMA (fill + read) and re-reads its operands from L2 for every tile;
@@ -267,7 +267,7 @@ TcPolicy tc_policy() {
     }();
     return v;
 }
-constexpr int kMinTcTiles = 120;
+constexpr int kMinTcTiles = 74;  // half the SMs of a B200: below that the persistent grid leaves most of the GPU idle
 bool use_tc_kernel(int M, int N, int K, bool unaligned_result) {
     if (tc_policy() == TcPolicy::kNever || b200gemm::tc_gemm_tiles(M, N) < kMinTcTiles) return false;
     if (tc_policy() == TcPolicy::kAlways) return true;
