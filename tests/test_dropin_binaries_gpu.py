@@ -128,7 +128,7 @@ def test_gemm_wrappers_against_host_fp64(mode, tol, kernel):
     tail = json.loads(res.stdout.strip().splitlines()[-1])
     assert tail["device_fault"] == 0
     # seven of the cases are large enough for the hand-written kernel; "library" never runs it
-    assert tail["tcgen05_kernel_launches"] == {"tcgen05": 7, "auto": 2, "library": 0}[kernel], tail
+    assert tail["tcgen05_kernel_launches"] == {"tcgen05": 7, "auto": 3, "library": 0}[kernel], tail
 
 
 def test_staged_operand_reuse_between_the_backward_pair():

@@ -4,10 +4,10 @@
 // in place of the library call when B200GEMM_KERNEL=tcgen05.
 //
 //   * One persistent CTA per SM walks 256 x 256 output tiles (M fastest, so the CTAs running together share one
-//     256-column panel of B in L2). 192 threads in three roles: warp 4 issues TMA loads (cp.async.bulk.tensor, 128-byte
-//     swizzle, no multicast) into a three-stage ring of 64 KB (A 256 x 64, B 256 x 64); one thread of warp 5 issues
+//     256-column panel of B in L2). 320 threads in three roles: warp 8 issues TMA loads (cp.async.bulk.tensor, 128-byte
+//     swizzle, no multicast) into a three-stage ring of 64 KB (A 256 x 64, B 256 x 64); one thread of warp 9 issues
 //     tcgen05.mma (M = 128, N = 256, K = 16; two per K step, one for each half of the tile's rows, both reading the same
-//     B tile); warps 0-3 are the epilogue.
+//     B tile); warps 0-7 are the epilogue.
 //   * Why 256 x 256: what paces a one-CTA GEMM on this part is the L2 -> SM path, not the tensor pipe. With 128 x 256
 //     tiles (and a double-buffered accumulator) this kernel moved 48 KB per 512 cycles of MMA and ran at 41 % of the MMA
 //     rate with 9.8 TB/s of L2 reads (measured on the K = 50257 product of the head: about 38 B/clk per SM); a 256 x 256
@@ -43,11 +43,11 @@ constexpr int kABytes = kBM * kBK * 2;      // 32 KB
 constexpr int kBBytes = kBN * kBK * 2;      // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAtom64Bytes = 64 * 128;      // a 64-row x 64-element box: 8 KB
-constexpr int kEpiWarps = 4;
-constexpr int kEpiPitch = 36;               // floats per staged row: 16-byte stores and conflict-free column reads
+constexpr int kEpiWarps = 8;                // two per scheduler: a lone warp cannot hide its own load -> store latency
+constexpr int kEpiPitch = 33;               // floats per staged row: conflict-free transposition
 constexpr int kEpiBytes = kEpiWarps * 32 * kEpiPitch * 4;
-constexpr int kProducerWarp = 4, kMmaWarp = 5;
-constexpr int kThreads = 192;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 320;
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;  // + slack for the 1024-byte alignment of the ring
 
 __device__ unsigned int g_fault_word;
@@ -147,29 +147,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             }
         }
     } else {
-        // epilogue: warp w owns TMEM lanes [32w, 32w + 32) = rows 32w ... of either half of the tile
+        // epilogue: warp w reads TMEM lanes [32 (w % 4), +32) (the quadrant a warp may access) = rows 32 (w % 4) ... of either
+        // half of the tile, and takes every other 32-column chunk (w / 4 selects which)
         float* stage = epi + warp * 32 * kEpiPitch;
+        const int quad = warp & 3, phase = warp >> 2;
         int lt = 0;
         for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
             const int n0 = (t / m_tiles) * kBN;
             mbar_wait(&acc_full, lt & 1, &abort_flag, fault, 0x63);
             tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < 2 * (kBN / 32); ++c) {
+            for (int c = phase; c < 2 * (kBN / 32); c += 2) {
                 const int half = c / (kBN / 32), cc = c % (kBN / 32);  // accumulator (row half), 32-column chunk
-                const int m0 = (t % m_tiles) * kBM + half * 128 + warp * 32;
+                const int m0 = (t % m_tiles) * kBM + half * 128 + quad * 32;
                 uint32_t v[32];
-                tmem_ld32(tmem_addr(tmem, warp * 32, half * kBN + cc * 32), v);
+                tmem_ld32(tmem_addr(tmem, quad * 32, half * kBN + cc * 32), v);
                 tmem_wait_ld();
-                if (c == 2 * (kBN / 32) - 1) {  // both accumulators have been read completely: hand them back to the MMA warp
+                if (c + 2 >= 2 * (kBN / 32)) {  // this warp has read its share of both accumulators
                     tc_fence_before();
                     mbar_arrive(&acc_empty);
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    *reinterpret_cast<float4*>(stage + lane * kEpiPitch + 4 * j) =
-                        make_float4(__uint_as_float(v[4 * j]) * a.alpha, __uint_as_float(v[4 * j + 1]) * a.alpha,
-                                    __uint_as_float(v[4 * j + 2]) * a.alpha, __uint_as_float(v[4 * j + 3]) * a.alpha);
+                for (int j = 0; j < 32; ++j) stage[lane * kEpiPitch + j] = __uint_as_float(v[j]) * a.alpha;
                 __syncwarp();
                 float o[32];
 #pragma unroll

@@ -249,14 +249,14 @@ bool stage_all() {
     return v;
 }
 // Which staged products go to the hand-written tcgen05 kernel (gemm_tc.cu) instead of the library:
-//   B200GEMM_KERNEL=auto (default)  those it wins: a result with an unaligned leading dimension that is larger than the
-//                                   operands (the language-model-head forward: 3.3 GB of logits written in place instead
-//                                   of into a padded tile and copied; measured 1.73 against 2.20 ms)
+//   B200GEMM_KERNEL=auto (default)  those it wins: results with an unaligned leading dimension, which it writes in place
+//                                   where the library path needs a padded tile and a copy back (the language-model head:
+//                                   forward 1.79 against 2.20 ms, weight gradient 1.50 against 1.59 ms, staging included)
 //   B200GEMM_KERNEL=tcgen05         every staged product with at least 74 output tiles (256 x 256) and no epilogue
 //   B200GEMM_KERNEL=library         none
-// Elsewhere the library's two-CTA kernels are faster: a one-CTA kernel with both operands in shared memory moves 96 KB
-// through the 128 B/clk port per 512 cycles of MMA (fill + read) and re-reads its operands from L2 for every tile;
-// measured 540-740 TFLOP/s against 750-1100 for the library on the layer shapes.
+// Elsewhere the library's two-CTA kernels are faster (layer shapes, K = 768 ... 3072: 510-570 TFLOP/s against 750-1100,
+// staging included): this kernel's main loop keeps the tensor pipe at 92 % of its rate, but its epilogue - 256 KB of FP32
+// per tile, not overlapped with the next tile's MMAs - drains at about 10 B/clk per SM.
 enum class TcPolicy { kAuto, kAlways, kNever };
 TcPolicy tc_policy() {
     static const TcPolicy v = [] {
@@ -271,7 +271,8 @@ constexpr int kMinTcTiles = 74;  // half the SMs of a B200: below that the persi
 bool use_tc_kernel(int M, int N, int K, bool unaligned_result) {
     if (tc_policy() == TcPolicy::kNever || b200gemm::tc_gemm_tiles(M, N) < kMinTcTiles) return false;
     if (tc_policy() == TcPolicy::kAlways) return true;
-    return unaligned_result && (double)M * N >= (double)K * ((double)M + N);
+    (void)K;
+    return unaligned_result;
 }
 
 // Products below this many multiply-adds are never staged (B200GEMM_STAGE_MIN_MACS overrides the default 2^30, for tests
