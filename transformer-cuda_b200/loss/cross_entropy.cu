@@ -34,6 +34,11 @@
 #include "b200loss.h"
 #include "tc_common.cuh"
 
+// Defined by the GEMM drop-in (libb200gemm.a) when it is linked into the same program and B200GEMM_TWINS=1, else NULL: a
+// BF16 twin of d_logits (rows of round_up(V, 8) elements), written here beside the FP32 values so that the two head
+// GEMMs of the backward pass, which read d_logits next, convert nothing.
+extern "C" void* b200gemm_bf16_twin(const void* fp32, int rows, int cols) __attribute__((weak));
+
 namespace {
 
 using namespace b200attn;
@@ -111,7 +116,8 @@ __device__ void finish_mean_loss(const float* row_loss, int rows, float* loss_ou
 // words[0] = ticket of finished CTAs, words[1] = record of a wait that ran out
 __global__ void __launch_bounds__(kThreads, 1)
     cross_entropy_resident_kernel(const float* __restrict__ logits, const int* __restrict__ targets, float* dlogits,
-                                  float* row_loss, float* loss_out, unsigned int* words, int rows, int V, float scale) {
+                                  float* row_loss, float* loss_out, unsigned int* words, int rows, int V, float scale,
+                                  __nv_bfloat16* __restrict__ twin, int twin_ld) {
     extern __shared__ __align__(128) float buf[];  // the interior of the current row
     __shared__ uint64_t load_bar[kMaxChunks];
     __shared__ float red_max[32], red_sum[32];
@@ -191,7 +197,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 
         // pass 3: d_logits, chunk by chunk into the bulk stores; the next row's loads follow kLag chunks behind
         const float k = scale / (sum + 1e-12f);
-        if (edge >= 0) dst[edge] = fmaf(edge_x, k, edge == target ? -scale : 0.f);
+        __nv_bfloat16* trow = twin ? twin + (long long)row * twin_ld : nullptr;
+        if (edge >= 0) {
+            const float d = fmaf(edge_x, k, edge == target ? -scale : 0.f);
+            dst[edge] = d;
+            if (trow) trow[edge] = __float2bfloat16_rn(d);
+        }
         const int next = row + gridDim.x;
         const bool has_next = next < rows;
         const RowGeom gn = row_geom(has_next ? next : row, V);
@@ -206,6 +217,16 @@ __global__ void __launch_bounds__(kThreads, 1)
                 x.x -= at == 0 ? scale : 0.f, x.y -= at == 1 ? scale : 0.f;
                 x.z -= at == 2 ? scale : 0.f, x.w -= at == 3 ? scale : 0.f;
                 *p = x;
+                if (trow) {  // v0 = head (mod 4): 4-byte aligned pairs when the head is even, else one element on each side
+                    if ((v0 & 1) == 0) {
+                        *reinterpret_cast<__nv_bfloat162*>(trow + v0) = __floats2bfloat162_rn(x.x, x.y);
+                        *reinterpret_cast<__nv_bfloat162*>(trow + v0 + 2) = __floats2bfloat162_rn(x.z, x.w);
+                    } else {
+                        trow[v0] = __float2bfloat16_rn(x.x);
+                        *reinterpret_cast<__nv_bfloat162*>(trow + v0 + 1) = __floats2bfloat162_rn(x.y, x.z);
+                        trow[v0 + 3] = __float2bfloat16_rn(x.w);
+                    }
+                }
             }
             fence_proxy_async_smem();
             __syncthreads();
@@ -248,7 +269,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 constexpr int kStreamThreads = 512;
 __global__ void __launch_bounds__(kStreamThreads)
     cross_entropy_stream_kernel(const float* __restrict__ logits, const int* __restrict__ targets, float* dlogits,
-                                float* row_loss, float* loss_out, unsigned int* words, int rows, int V, float scale) {
+                                float* row_loss, float* loss_out, unsigned int* words, int rows, int V, float scale,
+                                __nv_bfloat16* __restrict__ twin, int twin_ld) {
     __shared__ float red_max[32], red_sum[32];
     __shared__ double red_loss[32];
     __shared__ uint32_t is_last;
@@ -283,8 +305,11 @@ __global__ void __launch_bounds__(kStreamThreads)
     }
     const float k = scale / (sum + 1e-12f), m2 = gmax * kLog2e;
     __syncthreads();  // the row's logits are read for the last time above when d_logits aliases logits
-    for (int v = tid; v < V; v += kStreamThreads)
-        dst[v] = fmaf(fast_exp2(fmaf(src[v], kLog2e, -m2)), k, v == target ? -scale : 0.f);
+    for (int v = tid; v < V; v += kStreamThreads) {
+        const float d = fmaf(fast_exp2(fmaf(src[v], kLog2e, -m2)), k, v == target ? -scale : 0.f);
+        dst[v] = d;
+        if (twin) twin[(long long)row * twin_ld + v] = __float2bfloat16_rn(d);
+    }
 
     if (row_loss != nullptr) {
         __syncthreads();
@@ -358,6 +383,8 @@ int launch(const float* logits, const int* targets, float* dlogits, float* devic
     if (loss_location) *loss_location = loss_out;
     float* row_loss = want_loss ? s.row_loss : nullptr;
     const float scale = 1.0f / (float)rows;
+    __nv_bfloat16* twin = b200gemm_bf16_twin ? static_cast<__nv_bfloat16*>(b200gemm_bf16_twin(dlogits, rows, V)) : nullptr;
+    const int twin_ld = (V + 7) / 8 * 8;
     if (resident_path(logits, dlogits, V)) {
         if (!s.attr_set) {
             e = cudaFuncSetAttribute(cross_entropy_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxResidentV * 4);
@@ -367,10 +394,10 @@ int launch(const float* logits, const int* targets, float* dlogits, float* devic
         const int smem = ((V + 3) & ~3) * 4;
         const int grid = rows < s.sm_count ? rows : s.sm_count;
         cross_entropy_resident_kernel<<<grid, kThreads, smem, stream>>>(logits, targets, dlogits, row_loss, loss_out, s.words,
-                                                                        rows, V, scale);
+                                                                        rows, V, scale, twin, twin_ld);
     } else {
         cross_entropy_stream_kernel<<<rows, kStreamThreads, 0, stream>>>(logits, targets, dlogits, row_loss, loss_out, s.words,
-                                                                         rows, V, scale);
+                                                                         rows, V, scale, twin, twin_ld);
     }
     if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail("kernel launch", e);
     return B200LOSS_OK;
