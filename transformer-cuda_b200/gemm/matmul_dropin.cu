@@ -256,7 +256,7 @@ bool stage_all() {
 //   B200GEMM_KERNEL=library         none
 // Elsewhere the library's two-CTA kernels are faster (layer shapes, K = 768 ... 3072: 510-570 TFLOP/s against 750-1100,
 // staging included): this kernel's main loop keeps the tensor pipe at 92 % of its rate, but its epilogue - 256 KB of FP32
-// per tile, not overlapped with the next tile's MMAs - drains at about 10 B/clk per SM.
+// per tile - is not overlapped with the next tile's MMAs (both accumulators are in use).
 enum class TcPolicy { kAuto, kAlways, kNever };
 TcPolicy tc_policy() {
     static const TcPolicy v = [] {
