@@ -394,11 +394,12 @@ class DeviceWorkload:
     """Seeded BF16 Q, K, V, dO of one workload resident on one GPU (this rank's (batch, head) slabs of a batch
     `world` times the per-GPU batch), rotating over enough buffer sets to exceed L2, and the forward + backward step."""
 
-    def __init__(self, pkg, dev, rank, world, B, H, T, d):
+    def __init__(self, pkg, dev, rank, world, B, H, T, d, strong=False):
         import torch
         self.pkg, self.ops, self.dev, self.torch = pkg, pkg.ops, dev, torch
         ops = self.ops
-        mine = pkg.shard.slab_range(B * H * world, rank, world)
+        # weak: every rank holds one full per-GPU workload; strong: the ranks share the B * H slabs of ONE workload
+        mine = pkg.shard.slab_range(B * H * (1 if strong else world), rank, world)
         self.BH, self.T, self.d = mine.count, T, d
         self.n = self.BH * T * d
         self.scale = 1.0 / math.sqrt(d)
@@ -469,9 +470,13 @@ def extra_workloads(pkg, dev, rank, world, local, peaks, names):
     import torch
     from transformer_cuda_b200 import dist as pdist
     out = {}
-    for name in names:
+    # with more than one GPU, the fixed-size problems sharded by (batch, head) as well: strong scaling of c2 and c3
+    runs = [(n, False) for n in names] + ([(n, True) for n in ("c2", "c3") if world > 1 and n in WORKLOADS])
+    for name, strong in runs:
         B, H, T, d = WORKLOADS[name]
-        W = DeviceWorkload(pkg, dev, rank, world, B, H, T, d)
+        if strong and B * H < world:
+            continue
+        W = DeviceWorkload(pkg, dev, rank, world, B, H, T, d, strong=strong)
         # calibrate the step count on three untimed steps
         for i in range(3):
             W.step(W.sets[i % W.n_sets])
@@ -491,7 +496,10 @@ def extra_workloads(pkg, dev, rank, world, local, peaks, names):
         fl = pdist.sum_over_ranks(flops(1, W.BH, T, d), device=dev)
         value = fl / (ms * 1e-3) / 1e12
         bwd_ms, fwd_ms, bwd_tf, fwd_tf = kernel_rooflines(kt, W.BH, T, d, peaks)
-        out[name] = {"workload": f"B={B} H={H} T={T} d={d} per GPU", "steps": steps, "warmup": 6, "ms_per_step": ms,
+        out[name + "_strong" if strong else name] = {
+                     "workload": f"B={B} H={H} T={T} d={d} " + (f"in total, {W.BH} of its {B * H} (batch, head) slabs on each of {world} GPUs"
+                                                            if strong else "per GPU"),
+                     "scaling": "strong" if strong else "weak", "steps": steps, "warmup": 6, "ms_per_step": ms,
                      "value": value, "unit": UNIT, "frac_of_bf16_peak": value / world / peaks["bf16"],
                      "frac_of_bf16_sustained_peak": value / world / peaks["bf16_sustained"],
                      "bwd_kernel": {"launch_ms": bwd_ms, "achieved": bwd_tf, "frac": bwd_tf / peaks["bf16"],
