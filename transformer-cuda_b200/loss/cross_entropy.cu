@@ -21,17 +21,13 @@
 //     in double precision, and writes the mean: the result does not depend on the order CTAs ran in, and the host
 //     reads 4 bytes instead of B * T floats (src/kernels/loss.cu:116-124 copies them all and sums on the host).
 //
-// Rows of up to 51200 logits take a second form of the same idea (cross_entropy_register_kernel, further down): the row
-// is held in registers, shared memory is only the landing zone of the copies, and the next row's loads overlap this row's
-// arithmetic and stores completely. Rows that do not fit shared memory (V > 57344), V < 8 or buffers that are not 16-byte aligned take a streaming
+// Rows that do not fit shared memory (V > 57344), V < 8 or buffers that are not 16-byte aligned take a streaming
 // kernel: one CTA per row, an online (max, sum) pass and a second pass that writes d_logits - two reads instead of
 // the reference's three. Every mbarrier wait is bounded (tc_common.cuh); no cluster-wide copy is used.
 #include "kernels/loss.cuh"
 
 #include <cfloat>
 #include <cstdio>
-#include <cstdlib>
-#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -269,167 +265,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
-// Rows of at most 51200 logits: the row lives in REGISTERS (256 threads x 50 float4) and shared memory is only where the
-// bulk copies land. A thread copies its float4 of a chunk into registers as soon as the chunk has arrived and hands the
-// chunk back at once (an mbarrier the producer warp waits on), so the loads of the CTA's NEXT row stream in during the
-// exponential and store passes of this one, and d_logits leave as 16-byte stores straight from registers: the CTA
-// always has copies outstanding. (In the kernel above the next row's loads can only start once this row's bulk stores
-// have read the single row buffer; its exponential pass runs with nothing in flight.)
-constexpr int kRegThreads = 256;             // compute threads; warp 8 is the producer
-constexpr int kRegChunk = 4 * kRegThreads;   // 1024 floats = 4 KB per bulk copy
-constexpr int kRegMaxChunks = 50;
-constexpr int kRegMaxV = kRegMaxChunks * kRegChunk;
-constexpr unsigned kWaitIdFree = 0x4d00u;
-
-__device__ __forceinline__ int reg_chunks(const RowGeom& g) { return (g.inter + kRegChunk - 1) / kRegChunk; }
-
-// 288 threads x 224 registers fill the register file of an SM (the launch-bounds heuristic would stop at 168 and spill)
-__global__ void __maxnreg__(224)
-    cross_entropy_register_kernel(const float* __restrict__ logits, const int* __restrict__ targets, float* dlogits,
-                                  float* row_loss, float* loss_out, unsigned int* words, int rows, int V, float scale,
-                                  __nv_bfloat16* __restrict__ twin, int twin_ld) {
-    extern __shared__ __align__(128) float buf[];
-    __shared__ uint64_t load_bar[kRegMaxChunks], free_bar[kRegMaxChunks];
-    __shared__ float red_max[8], red_sum[8];
-    __shared__ double red_loss[32];
-    __shared__ float target_logit;
-    __shared__ uint32_t abort_flag, is_last;
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int max_chunks = (V + kRegChunk - 1) / kRegChunk;  // chunks of the longest interior any row can have
-    if (tid == 0) {
-        for (int c = 0; c < kRegMaxChunks; ++c) mbar_init(&load_bar[c], 1), mbar_init(&free_bar[c], kRegThreads);
-        abort_flag = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-
-    if (warp == kRegThreads / 32) {
-        // producer: the rows of this CTA in order; chunk c of a row goes in once every compute thread has taken chunk c
-        // of the row before into its registers
-        if (lane == 0) {
-            int it = 0;
-            for (int row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
-                const RowGeom g = row_geom(row, V);
-                const int nc = reg_chunks(g);
-                const float* src = logits + g.start + g.head;
-                for (int c = 0; c < max_chunks; ++c) {
-                    if (it > 0) mbar_wait_compact(&free_bar[c], (it - 1) & 1, &abort_flag, words + 1, kWaitIdFree + c, 0);
-                    if (c < nc) bulk_load(buf + c * kRegChunk, src + (long long)c * kRegChunk, min(kRegChunk, g.inter - c * kRegChunk) * 4, &load_bar[c]);
-                }
-            }
-        }
-    } else {
-        uint64_t phases = 0;  // bit c: parity the next wait on load_bar[c] uses
-        for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-            const RowGeom g = row_geom(row, V);
-            const int nc = reg_chunks(g);
-            const float* src = logits + g.start;
-            float* dst = dlogits + g.start;
-            const int target = targets[row];
-            const int edge = tid < g.head ? tid : (tid >= 32 && tid < 32 + g.tail) ? g.head + g.inter + (tid - 32) : -1;
-            float edge_x = edge >= 0 ? src[edge] : -FLT_MAX;
-            if (tid == 0) target_logit = 0.f;
-
-            // pass 1: the row into registers, chunk by chunk as the copies land; running maximum
-            float4 x[kRegMaxChunks];
-            float m = edge_x;
-#pragma unroll
-            for (int c = 0; c < kRegMaxChunks; ++c) {
-                x[c] = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
-                if (c < max_chunks) {
-                    if (c < nc) {
-                        mbar_wait_compact(&load_bar[c], (uint32_t)(phases >> c) & 1u, &abort_flag, words + 1, kWaitIdLoad + c, 0);
-                        phases ^= 1ull << c;
-                        if (tid * 4 < g.inter - c * kRegChunk) x[c] = *reinterpret_cast<const float4*>(buf + c * kRegChunk + tid * 4);
-                    }
-                    m = fmaxf(m, fmaxf(fmaxf(x[c].x, x[c].y), fmaxf(x[c].z, x[c].w)));  // (also: the load has returned)
-                    mbar_arrive(&free_bar[c]);
-                }
-            }
-            m = warp_max(m);
-            if (lane == 0) red_max[warp] = m;
-            named_bar_sync(1, kRegThreads);
-            m = red_max[lane & 7];
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-            const float m2 = m * kLog2e;
-
-            // pass 2: exponentials in registers, their sum, the target's logit
-            float sum = 0.f;
-            if (edge >= 0) {
-                if (edge == target) target_logit = edge_x - m;
-                edge_x = fast_exp2(fmaf(edge_x, kLog2e, -m2));
-                sum = edge_x;
-            }
-#pragma unroll
-            for (int c = 0; c < kRegMaxChunks; ++c) {
-                if (c < nc && tid * 4 < g.inter - c * kRegChunk) {
-                    const int at = target - (g.head + c * kRegChunk + tid * 4);
-                    if ((unsigned)at < 4u) target_logit = (at == 0 ? x[c].x : at == 1 ? x[c].y : at == 2 ? x[c].z : x[c].w) - m;
-                    x[c].x = fast_exp2(fmaf(x[c].x, kLog2e, -m2));
-                    x[c].y = fast_exp2(fmaf(x[c].y, kLog2e, -m2));
-                    x[c].z = fast_exp2(fmaf(x[c].z, kLog2e, -m2));
-                    x[c].w = fast_exp2(fmaf(x[c].w, kLog2e, -m2));
-                    sum += (x[c].x + x[c].y) + (x[c].z + x[c].w);
-                }
-            }
-            sum = warp_sum(sum);
-            if (lane == 0) red_sum[warp] = sum;
-            named_bar_sync(1, kRegThreads);
-            sum = red_sum[lane & 7];
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-            if (tid == 0 && row_loss != nullptr) row_loss[row] = logf(sum) - target_logit;
-
-            // pass 3: d_logits straight from registers (the interior of a row is 16-byte aligned)
-            const float k = scale / (sum + 1e-12f);
-            __nv_bfloat16* trow = twin ? twin + (long long)row * twin_ld : nullptr;
-            if (edge >= 0) {
-                const float d = fmaf(edge_x, k, edge == target ? -scale : 0.f);
-                dst[edge] = d;
-                if (trow) trow[edge] = __float2bfloat16_rn(d);
-            }
-#pragma unroll
-            for (int c = 0; c < kRegMaxChunks; ++c) {
-                if (c < nc && tid * 4 < g.inter - c * kRegChunk) {
-                    const int v0 = g.head + c * kRegChunk + tid * 4, at = target - v0;
-                    float4 r = make_float4(x[c].x * k, x[c].y * k, x[c].z * k, x[c].w * k);
-                    r.x -= at == 0 ? scale : 0.f, r.y -= at == 1 ? scale : 0.f;
-                    r.z -= at == 2 ? scale : 0.f, r.w -= at == 3 ? scale : 0.f;
-                    __stcs(reinterpret_cast<float4*>(dst + v0), r);
-                    if (trow) {
-                        if ((v0 & 1) == 0) {
-                            *reinterpret_cast<__nv_bfloat162*>(trow + v0) = __floats2bfloat162_rn(r.x, r.y);
-                            *reinterpret_cast<__nv_bfloat162*>(trow + v0 + 2) = __floats2bfloat162_rn(r.z, r.w);
-                        } else {
-                            trow[v0] = __float2bfloat16_rn(r.x);
-                            *reinterpret_cast<__nv_bfloat162*>(trow + v0 + 1) = __floats2bfloat162_rn(r.y, r.z);
-                            trow[v0 + 3] = __float2bfloat16_rn(r.w);
-                        }
-                    }
-                }
-            }
-        }
-    }
-
-    if (row_loss != nullptr) {
-        __syncthreads();
-        if (tid == 0) {
-            __threadfence();
-            is_last = atomicAdd(words, 1u) == gridDim.x - 1 ? 1u : 0u;
-        }
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            finish_mean_loss(row_loss, rows, loss_out, red_loss);
-            if (tid == 0) words[0] = 0u;
-        }
-    }
-}
-
 // Any V, any alignment: one CTA per row, online (max, sum), then the write pass.
 constexpr int kStreamThreads = 512;
 __global__ void __launch_bounds__(kStreamThreads)
@@ -499,7 +334,7 @@ struct DeviceScratch {
     size_t rows_cap = 0;
     unsigned int* words = nullptr;  // ticket, fault record, [2] = loss when the caller keeps none
     int sm_count = 0;
-    bool attr_set = false, reg_attr_set = false;
+    bool attr_set = false;
 };
 constexpr int kMaxDevices = 64;
 DeviceScratch g_scratch[kMaxDevices];
@@ -515,14 +350,6 @@ int cuda_fail(const char* what, cudaError_t e) {
 
 bool resident_path(const float* logits, const float* dlogits, int V) {
     return V >= 8 && V <= kMaxResidentV && ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15u) == 0;
-}
-// B200LOSS_KERNEL=shared keeps rows that would fit the register kernel on the shared-memory one (for comparison runs).
-bool register_path(int V) {
-    static const bool allowed = [] {
-        const char* e = getenv("B200LOSS_KERNEL");
-        return !(e && !strcmp(e, "shared"));
-    }();
-    return allowed && V <= kRegMaxV;
 }
 
 int launch(const float* logits, const int* targets, float* dlogits, float* device_loss, bool want_loss, int B, int T,
@@ -558,17 +385,7 @@ int launch(const float* logits, const int* targets, float* dlogits, float* devic
     const float scale = 1.0f / (float)rows;
     __nv_bfloat16* twin = b200gemm_bf16_twin ? static_cast<__nv_bfloat16*>(b200gemm_bf16_twin(dlogits, rows, V)) : nullptr;
     const int twin_ld = (V + 7) / 8 * 8;
-    if (resident_path(logits, dlogits, V) && register_path(V)) {
-        if (!s.reg_attr_set) {
-            e = cudaFuncSetAttribute(cross_entropy_register_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRegMaxV * 4);
-            if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
-            s.reg_attr_set = true;
-        }
-        const int smem = (V + kRegChunk - 1) / kRegChunk * kRegChunk * 4;
-        const int grid = rows < s.sm_count ? rows : s.sm_count;
-        cross_entropy_register_kernel<<<grid, kRegThreads + 32, smem, stream>>>(logits, targets, dlogits, row_loss, loss_out, s.words,
-                                                                               rows, V, scale, twin, twin_ld);
-    } else if (resident_path(logits, dlogits, V)) {
+    if (resident_path(logits, dlogits, V)) {
         if (!s.attr_set) {
             e = cudaFuncSetAttribute(cross_entropy_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxResidentV * 4);
             if (e != cudaSuccess) return cuda_fail("cudaFuncSetAttribute", e);
