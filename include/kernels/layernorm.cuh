@@ -19,3 +19,10 @@ void layernorm_forward(const float* x, const float* gamma, const float* beta, fl
 void layernorm_backward(const float* dout, const float* x, const float* gamma, const float* mean, const float* rstd,
                         float* dx, float* dgamma, float* dbeta, int N, int C, const float* residual_add = nullptr,
                         bool accumulate = false, cudaStream_t stream = 0);
+
+// Extension (not in the reference's header): a host callback run after every layernorm_backward launch, with the number
+// of layernorm_backward calls since the last reset (1, 2, ...), the stream and `user`. A data-parallel trainer uses it to
+// start the all-reduce of the gradients that are final at that point of the model's backward pass
+// (transformer-cuda_b200/harness/gpt_step_dp.cu). NULL removes the hook.
+extern "C" void b200norm_set_backward_hook(void (*fn)(int call_index, cudaStream_t stream, void* user), void* user);
+extern "C" void b200norm_reset_backward_count(void);

@@ -97,3 +97,17 @@ def test_two_ranks_average_their_gradients():
     assert two["n_gpus"] == 2 and two["allreduce_ms_per_step"] > 0.0
     assert two["loss"] == two["loss"] and abs(two["loss"] - one["loss"]) <= 0.5  # finite, same regime (ln 257 = 5.55 at init)
     assert two["value"] > 0
+
+
+def test_overlapped_bucketed_allreduce_matches_the_single_one():
+    """Two ranks, every drop-in: with the gradient all-reduce issued part by part behind the LayerNorm backward calls
+    that complete each part (on a second stream, overlapping the rest of the backward pass), the loss after three
+    steps is the one of the run with a single all-reduce after the backward pass; the line says which was used."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    exe = _binary("gpt_step_dp_b200_all")
+    env = {"B200ATTN_MATH": "fp32", "B200GEMM_MATH": "fp32", "NCCL_NVLS_ENABLE": "0"}
+    single = _run(exe, dict(env, B200_DP_OVERLAP="0"), world=2)
+    bucketed = _run(exe, dict(env, B200_DP_OVERLAP="1"), world=2)
+    assert single["allreduce_overlapped"] is False and bucketed["allreduce_overlapped"] is True
+    assert abs(bucketed["loss"] - single["loss"]) <= 1e-4 * max(1.0, abs(single["loss"])), (bucketed["loss"], single["loss"])

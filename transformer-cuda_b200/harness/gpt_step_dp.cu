@@ -57,6 +57,34 @@ extern "C" long long b200gemm_tc_launches(void) __attribute__((weak));
 extern "C" long long b200gemm_staged_reuses(void) __attribute__((weak));
 extern "C" long long b200gemm_twin_hits(void) __attribute__((weak));
 
+// Hook of the LayerNorm drop-in (weak: builds that link the reference's own layernorm.cu have none).
+extern "C" void b200norm_set_backward_hook(void (*fn)(int, cudaStream_t, void*), void* user) __attribute__((weak));
+extern "C" void b200norm_reset_backward_count(void) __attribute__((weak));
+
+// Bucketed all-reduce overlapped with the backward pass. The gradient buffer is laid out [embeddings | layer 0 ... layer
+// L-1 | final LayerNorm | head] (src/model.cu:45-58) and the backward pass finishes those parts from the back: head and
+// final LayerNorm first (done once the final LayerNorm's backward has been launched: the 1st layernorm_backward call), then
+// layer L-1 (its LN1 backward is the 3rd call), ... layer 0 (call 1 + 2 L), the embeddings last. After each of those calls
+// the part that has just become final is all-reduced in place on a second stream, ordered behind the compute stream by an
+// event; the optimizer waits for the second stream. Every rank issues the same collectives in the same order.
+struct OverlapState {
+    ncclComm_t comm = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    float* base = nullptr;
+    std::vector<std::pair<size_t, size_t>> part_after_call;  // [call index] -> (offset, count); count 0: nothing
+    std::vector<cudaEvent_t> events;
+};
+static void reduce_part(OverlapState* o, size_t offset, size_t count, cudaEvent_t ev, cudaStream_t compute) {
+    CUDA_CHECK(cudaEventRecord(ev, compute));
+    CUDA_CHECK(cudaStreamWaitEvent(o->comm_stream, ev, 0));
+    NCCL_CHECK(ncclAllReduce(o->base + offset, o->base + offset, count, ncclFloat, ncclAvg, o->comm, o->comm_stream));
+}
+static void on_layernorm_backward(int call, cudaStream_t stream, void* user) {
+    OverlapState* o = static_cast<OverlapState*>(user);
+    if (call >= (int)o->part_after_call.size() || o->part_after_call[call].second == 0) return;
+    reduce_part(o, o->part_after_call[call].first, o->part_after_call[call].second, o->events[call], stream);
+}
+
 int main(int argc, char** argv) {
     int steps = 5, warmup = 2;
     TransformerConfig cfg;
@@ -142,13 +170,56 @@ int main(int argc, char** argv) {
     CUDA_CHECK(cudaMalloc(&d_time, sizeof(float)));
     float host_loss = 0.f;
 
-    // events around every all-reduce of the timed steps: the collective's share of a step is reported
+    // overlapped, bucketed all-reduce: needs the LayerNorm drop-in's hook; B200_DP_OVERLAP=0 keeps the single all-reduce
+    OverlapState overlap;
+    const bool use_overlap = world > 1 && b200norm_set_backward_hook != nullptr && env_int("B200_DP_OVERLAP", 1) != 0;
+    cudaEvent_t tail_event = nullptr, comm_done = nullptr;
+    size_t embeddings_count = 0;
+    if (use_overlap) {
+        const TransformerParameters& gp = model.get_gradients().params;
+        const int L = (int)cfg.num_layers;
+        overlap.comm = comm, overlap.base = model.get_grads_memory();
+        CUDA_CHECK(cudaStreamCreateWithFlags(&overlap.comm_stream, cudaStreamNonBlocking));
+        overlap.part_after_call.assign(2 * L + 2, std::make_pair(size_t(0), size_t(0)));
+        overlap.events.resize(2 * L + 2);
+        for (auto& e : overlap.events) CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        const size_t off_lnf = gp.ln_f_gamma - overlap.base;
+        overlap.part_after_call[1] = {off_lnf, n_params - off_lnf};  // final LayerNorm + head
+        for (int l = L - 1; l >= 0; --l) {
+            const size_t begin = gp.layers[l].ln1_gamma - overlap.base;
+            const size_t end = (l + 1 < L ? gp.layers[l + 1].ln1_gamma : gp.ln_f_gamma) - overlap.base;
+            overlap.part_after_call[1 + 2 * (L - l)] = {begin, end - begin};
+        }
+        embeddings_count = (L > 0 ? gp.layers[0].ln1_gamma : gp.ln_f_gamma) - overlap.base;
+        CUDA_CHECK(cudaEventCreateWithFlags(&tail_event, cudaEventDisableTiming));
+        CUDA_CHECK(cudaEventCreateWithFlags(&comm_done, cudaEventDisableTiming));
+        b200norm_set_backward_hook(on_layernorm_backward, &overlap);
+    }
+
+    // events around every all-reduce of the timed steps: the collective's share of a step is reported (with the overlap:
+    // the part of it the compute stream waits for after the backward pass)
     std::vector<cudaEvent_t> ar_events;
     bool time_allreduce = false;
     auto step = [&](float* loss) {
         model.forward(d_tok, stream);
+        if (use_overlap) b200norm_reset_backward_count();
         model.backward(d_tok, d_tgt, loss, stream);
-        if (world > 1) {
+        if (use_overlap) {
+            cudaEvent_t a0 = nullptr, a1 = nullptr;
+            if (time_allreduce) {
+                CUDA_CHECK(cudaEventCreate(&a0));
+                CUDA_CHECK(cudaEventCreate(&a1));
+                CUDA_CHECK(cudaEventRecord(a0, stream));
+            }
+            reduce_part(&overlap, 0, embeddings_count, tail_event, stream);  // the embeddings: final only now
+            CUDA_CHECK(cudaEventRecord(comm_done, overlap.comm_stream));
+            CUDA_CHECK(cudaStreamWaitEvent(stream, comm_done, 0));
+            if (time_allreduce) {
+                CUDA_CHECK(cudaEventRecord(a1, stream));
+                ar_events.push_back(a0);
+                ar_events.push_back(a1);
+            }
+        } else if (world > 1) {
             cudaEvent_t a0 = nullptr, a1 = nullptr;
             if (time_allreduce) {
                 CUDA_CHECK(cudaEventCreate(&a0));
@@ -204,10 +275,10 @@ int main(int argc, char** argv) {
                "\"warmup\": %d, \"ms_per_step\": %.3f, \"allreduce_ms_per_step\": %.3f, \"loss\": %.5f, \"attention\": \"%s\", \"params\": %zu, "
                "\"config\": {\"L\": %zu, \"C\": %zu, \"H\": %zu, \"d_ff\": %zu, \"V\": %zu, \"T\": %d, \"per_gpu_batch\": %d, "
                "\"optimizer\": \"AdamW lr=3e-4 betas=(0.9,0.95) wd=0.1 clip=1.0\", \"parallelism\": \"dp%d, one ncclAllReduce(avg) of the gradient buffer per step\"}, "
-               "\"gemm_dropin\": {\"linked\": %s, \"tcgen05_launches\": %lld, \"staged_reuses\": %lld, \"twin_hits\": %lld}}\n",
+               "\"allreduce_overlapped\": %s, \"gemm_dropin\": {\"linked\": %s, \"tcgen05_launches\": %lld, \"staged_reuses\": %lld, \"twin_hits\": %lld}}\n",
                (double)world * B * T / (ms_step * 1e-3), world, steps, warmup, ms_step, ar_ms / steps, host_loss, attn, n_params,
                cfg.num_layers, cfg.d_model, cfg.num_heads, cfg.d_ff, cfg.vocab_size, T, B, world,
-               b200gemm_tc_launches ? "true" : "false", b200gemm_tc_launches ? b200gemm_tc_launches() : 0LL,
+               use_overlap ? "true" : "false", b200gemm_tc_launches ? "true" : "false", b200gemm_tc_launches ? b200gemm_tc_launches() : 0LL,
                b200gemm_staged_reuses ? b200gemm_staged_reuses() : 0LL, b200gemm_twin_hits ? b200gemm_twin_hits() : 0LL);
     }
     if (comm) ncclCommDestroy(comm);

@@ -251,6 +251,18 @@ void report(const char* what) {
     if (e != cudaSuccess) fprintf(stderr, "[b200norm] %s: %s\n", what, cudaGetErrorString(e));
 }
 
+// Called after every layernorm_backward with the number of such calls since the last reset. In the reference model's
+// backward pass the k-th LayerNorm backward marks the point where the gradients of another part of the model are final
+// (src/model.cu:478-700: the final LayerNorm after the head, then LN2 and LN1 of each layer, last layer first), which is
+// what a data-parallel trainer needs to know to start reducing them while the rest of the pass still runs.
+void (*g_backward_hook)(int, cudaStream_t, void*) = nullptr;
+void* g_backward_hook_user = nullptr;
+int g_backward_calls = 0;
+void after_backward(cudaStream_t stream) {
+    const int index = ++g_backward_calls;
+    if (g_backward_hook) g_backward_hook(index, stream, g_backward_hook_user);
+}
+
 template <int kVec>
 void launch_backward_reg(const float* dout, const float* x, const float* gamma, const float* mean, const float* rstd, float* dx,
                          float* dgamma, float* dbeta, int N, const float* residual, bool accumulate, cudaStream_t stream) {
@@ -316,4 +328,10 @@ void layernorm_backward(const float* dout, const float* x, const float* gamma, c
     }
 #undef B200NORM_BWD
     report("layernorm_backward");
+    after_backward(stream);
 }
+
+extern "C" void b200norm_set_backward_hook(void (*fn)(int, cudaStream_t, void*), void* user) {
+    g_backward_hook = fn, g_backward_hook_user = user, g_backward_calls = 0;
+}
+extern "C" void b200norm_reset_backward_count(void) { g_backward_calls = 0; }
