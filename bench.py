@@ -217,7 +217,11 @@ def run_gpt_step(args):
                                      else "reference loss.cu and optimizer.cu"},
             "loss_after_last_step": child["loss"], "gemm_dropin": child.get("gemm_dropin"),
             "allreduce_ms_per_step": child.get("allreduce_ms_per_step"),
-            "allreduce": "one in-place ncclAllReduce(avg) of the 163 M-float gradient buffer per step, timed with CUDA events on rank 0"}
+            "allreduce_overlapped": child.get("allreduce_overlapped"),
+            "allreduce": ("in-place ncclAllReduce(avg) of the 163 M-float gradient buffer in 14 parts on a second stream, each issued when "
+                          "the backward pass has finished that part; allreduce_ms_per_step = what the compute stream still waits for (rank 0)")
+                         if child.get("allreduce_overlapped") else
+                         "one in-place ncclAllReduce(avg) of the 163 M-float gradient buffer per step, timed with CUDA events on rank 0"}
     if world == 1 and args.impl != "reference" and not args.no_cpu_baseline:
         # the reference's PyTorch twin of the whole step on the host cores (a port: the checkout is not on this machine)
         import torch
