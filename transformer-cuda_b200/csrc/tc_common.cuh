@@ -358,6 +358,29 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
     return r;
 }
 
+// Packed FP32 pairs (sm_100: one instruction for two FMAs / adds). The softmax loops are paced by instruction issue as much
+// as by the 16-per-clock exponential unit; pairing the scale-and-shift and the row-sum additions takes two of the
+// seven instructions per pair of scores away.
+__device__ __forceinline__ float2 fma2(float ax, float ay, float b, float c) {
+    uint64_t ra, rb, rc, rd;
+    float2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(ax), "f"(ay));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(rb) : "f"(b));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(rc) : "f"(c));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float bx, float by) {
+    uint64_t ra, rb, rd;
+    float2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(bx), "f"(by));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
