@@ -420,9 +420,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc64_kernel(const __grid
                 // chunk of the row: 32 scores -> 16 packed BF16 pairs of P^T
                 auto exp_chunk = [&](const uint32_t* sv, uint32_t* pk) {
 #pragma unroll
-                    for (int x = 0; x < 32; x += 2)
-                        pk[x >> 1] = pack_bf16x2(fast_exp2(__uint_as_float(sv[x]) * scale_log2),
-                                                 fast_exp2(__uint_as_float(sv[x + 1]) * scale_log2));
+                    for (int x = 0; x < 32; x += 2) {
+                        const float2 t = mul2(__uint_as_float(sv[x]), __uint_as_float(sv[x + 1]), scale_log2, scale_log2);
+                        pk[x >> 1] = pack_bf16x2(fast_exp2(t.x), fast_exp2(t.y));
+                    }
                 };
 #pragma unroll 1
                 for (int c = 0; c < 4; c += 2) {
@@ -524,8 +525,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_tc64_kernel(const __grid
 #pragma unroll
                     for (int x = 0; x < 16; ++x) {
                         const uint32_t w = pp[x];  // P^T of queries 2x (low half) and 2x+1 (high half)
-                        dsw[h * 16 + x] = pack_bf16x2(__uint_as_float(w << 16) * __uint_as_float(dv[2 * x]),
-                                                      __uint_as_float(w & 0xffff0000u) * __uint_as_float(dv[2 * x + 1]));
+                        const float2 t = mul2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u), __uint_as_float(dv[2 * x]),
+                                              __uint_as_float(dv[2 * x + 1]));
+                        dsw[h * 16 + x] = pack_bf16x2(t.x, t.y);
                     }
                 }
                 if (leader) T64(1, g, 3);

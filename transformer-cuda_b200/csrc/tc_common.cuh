@@ -371,6 +371,15 @@ __device__ __forceinline__ float2 fma2(float ax, float ay, float b, float c) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
     return d;
 }
+__device__ __forceinline__ float2 mul2(float ax, float ay, float bx, float by) {
+    uint64_t ra, rb, rd;
+    float2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(ax), "f"(ay));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(bx), "f"(by));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
 __device__ __forceinline__ float2 add2(float2 a, float bx, float by) {
     uint64_t ra, rb, rd;
     float2 d;
