@@ -105,3 +105,43 @@ def test_loss_library_exports_its_header(pkg):
     assert so.b200loss_cross_entropy(None, None, None, None, 1, 1, 8, None) == -1
     assert b"NULL" in so.b200loss_last_error()
     assert so.b200loss_max_resident_vocab() >= 50257
+
+
+def test_caller_dropin_headers_keep_reference_signatures():
+    """The headers of the callers' drop-ins declare the reference's launchers verbatim (names, parameter order, types,
+    default arguments: include/kernels/layernorm.cuh:9-36, ffn.cuh:7-33, matmul.cuh:10-81 of the reference), so its
+    model.cu compiles against them unchanged; and the static libraries define them."""
+    def text(name):
+        with open(os.path.join(ROOT, "include", "kernels", name)) as f:
+            return re.sub(r"\s+", " ", f.read())
+    expect = {
+        "layernorm.cuh": [
+            "void layernorm_forward(const float* x, const float* gamma, const float* beta, float* out, float* mean, float* rstd, int N, int C, float eps, cudaStream_t stream = 0);",
+            "void layernorm_backward(const float* dout, const float* x, const float* gamma, const float* mean, const float* rstd, float* dx, float* dgamma, float* dbeta, int N, int C, const float* residual_add = nullptr, bool accumulate = false, cudaStream_t stream = 0);",
+        ],
+        "ffn.cuh": [
+            "void gelu_forward(const float* x, float* y, int N, cudaStream_t stream = 0);",
+            "void add_bias_gelu_forward(const float* x, const float* bias, float* y, int M, int N, cudaStream_t stream = 0);",
+            "void gelu_backward(const float* dy, const float* x, float* dx, int N, cudaStream_t stream = 0);",
+        ],
+        "matmul.cuh": [
+            "void matmul_forward(cublasHandle_t handle, const float* A, const float* B, float* C, int M, int N, int K, bool transA = false, bool transB = false, float alpha = 1.0f, float beta = 0.0f, cudaStream_t stream = 0);",
+            "void add_bias(float* Y, const float* bias, int M, int N, cudaStream_t stream = 0);",
+        ],
+    }
+    for header, sigs in expect.items():
+        t = text(header)
+        for sig in sigs:
+            assert sig in t, (header, sig)
+    libdir = os.path.join(ROOT, "transformer-cuda_b200", "lib")
+    if not os.path.exists(os.path.join(libdir, "libb200norm.a")):
+        import __graft_entry__ as entry
+        entry.build()
+    defined = {"libb200norm.a": ["layernorm_forward(", "layernorm_backward(", "b200norm_set_backward_hook"],
+               "libb200ffn.a": ["gelu_forward(", "add_bias_gelu_forward(", "gelu_backward("],
+               "libb200gemm.a": ["matmul_forward(", "matmul_cublaslt(", "bias_backward(", "b200gemm_bf16_twin", "b200gemm::tc_gemm_bf16("],
+               "libb200loss.a": ["cross_entropy_forward_backward(", "b200loss_cross_entropy"]}
+    for lib, names in defined.items():
+        out = subprocess.run(["nm", "--defined-only", "-C", os.path.join(libdir, lib)], capture_output=True, text=True, check=True).stdout
+        for n in names:
+            assert n in out, (lib, n)
