@@ -58,7 +58,12 @@ def _worker(rank, world, port, out_dir):
         x, y = _data(rank, step)
         opt.zero_grad()
         torch.nn.functional.mse_loss(model(x), y).backward()
-        flat = pdist.average_gradients_(_flat_grads(model))       # the exchange: once, on the finished buffer
+        flat = _flat_grads(model)
+        if step % 2 == 0:
+            flat = pdist.average_gradients_(flat)                 # the exchange: once, on the finished buffer
+        else:                                                     # ... or part by part, in the order the harness uses
+            n = flat.numel()
+            flat = pdist.average_gradients_in_parts_(flat, pdist.gradient_parts(2, n // 4, n // 4, n - 3 * (n // 4)))
         _set_grads(model, flat)
         torch.nn.utils.clip_grad_norm_(model.parameters(), CLIP)  # global-norm clip sees the AVERAGED gradient
         opt.step()
@@ -91,3 +96,16 @@ def test_single_rank_is_a_no_op(pkg):
     from transformer_cuda_b200 import dist as pdist
     g = torch.arange(5, dtype=torch.float32)
     assert torch.equal(pdist.average_gradients_(g.clone()), g)
+
+
+def test_gradient_parts_tile_the_buffer_in_backward_order(pkg):
+    from transformer_cuda_b200 import dist as pdist
+    # GPT-2 small: embeddings 38 597 376 + 786 432, twelve layers of 7 087 872, final LayerNorm + head 1 536 + 38 597 376
+    parts = pdist.gradient_parts(12, 7087872, 38597376 + 786432, 1536 + 38597376)
+    assert len(parts) == 14 and sum(c for _, c in parts) == 163037184
+    assert parts[0] == (163037184 - 38598912, 38598912) and parts[-1] == (0, 39383808)
+    assert [o for o, _ in parts[1:13]] == [39383808 + l * 7087872 for l in range(11, -1, -1)]
+    g = torch.arange(10, dtype=torch.float32)
+    assert torch.equal(pdist.average_gradients_in_parts_(g.clone(), pdist.gradient_parts(2, 3, 2, 2)), g)
+    with pytest.raises(ValueError):
+        pdist.average_gradients_in_parts_(g.clone(), [(0, 4), (5, 5)])

@@ -82,3 +82,32 @@ def average_gradients_(flat_grads: torch.Tensor) -> torch.Tensor:
         flat_grads.mul_(1.0 / dist.get_world_size())
     return flat_grads
 
+
+
+def gradient_parts(num_layers: int, per_layer: int, embeddings: int, tail: int):
+    """The order in which the parts of the flat gradient buffer [embeddings | layer 0 ... layer L-1 | final LayerNorm +
+    head] become final during the reference model's backward pass (src/model.cu:431-704), as (offset, count) pairs:
+    the tail first (after the final LayerNorm's backward), then the layers from the last to the first (after each
+    layer's LN1 backward), the embeddings last. transformer-cuda_b200/harness/gpt_step_dp.cu all-reduces them in this
+    order on a second stream while the pass still runs; every rank must use the same order."""
+    total = embeddings + num_layers * per_layer + tail
+    parts = [(total - tail, tail)]
+    for layer in range(num_layers - 1, -1, -1):
+        parts.append((embeddings + layer * per_layer, per_layer))
+    parts.append((0, embeddings))
+    return [(o, c) for o, c in parts if c > 0]
+
+
+def average_gradients_in_parts_(flat_grads: torch.Tensor, parts) -> torch.Tensor:
+    """average_gradients_ issued part by part (the harness's overlapped form): the same result, as long as the parts
+    tile the buffer exactly once."""
+    covered = sorted(parts)
+    if sum(c for _, c in covered) != flat_grads.numel() or any(covered[i][0] + covered[i][1] != covered[i + 1][0]
+                                                                for i in range(len(covered) - 1)) or covered[0][0] != 0:
+        raise ValueError("the parts must tile the gradient buffer exactly once")
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        for offset, count in parts:
+            piece = flat_grads[offset:offset + count]
+            dist.all_reduce(piece, op=dist.ReduceOp.SUM)
+            piece.mul_(1.0 / dist.get_world_size())
+    return flat_grads
