@@ -427,9 +427,11 @@ class DeviceWorkload:
         ops.attention_forward_bf16(s["q"], s["k"], s["v"], scale, s["o"], s["lse"])
         ops.attention_backward_bf16(s["q"], s["k"], s["v"], s["o"], s["dO"], s["lse"], scale, s["dq"], s["dk"], s["dv"])
 
-    def timed_steps(self, steps, warmup, stride, sampler=None):
+    def timed_steps(self, steps, warmup, stride, sampler=None, after=0):
         """`warmup` untimed steps, then exactly `steps` steps between barrier + synchronize on both sides, CUDA events on
-        the launching stream, maximum over ranks. Returns (total ms, per-kernel event times)."""
+        the launching stream, maximum over ranks; every `stride`-th launch of each kernel inside the region and every
+        launch of `after` further steps behind it is bracketed with events of its own.
+        Returns (total ms, per-kernel event times)."""
         torch, ops = self.torch, self.ops
         from transformer_cuda_b200 import dist as pdist
         for i in range(warmup):
@@ -450,8 +452,29 @@ class DeviceWorkload:
         pdist.barrier()
         ms_total = pdist.max_over_ranks(e0.elapsed_time(e1), device=self.dev)
         kt = ops.kernel_times()
+        # further steps right after the timed region, same buffers and stream, every launch bracketed: the events that
+        # cost the timed region its back-to-back launches cost nothing here, so short runs still get enough samples
+        kt["region_bwd_launches"], kt["region_fwd_launches"] = kt["bwd_launches"], kt["fwd_launches"]
+        if after > 0:
+            ops.kernel_timing(True, every=1)
+            for i in range(after):
+                self.step(self.sets[(steps + i) % self.n_sets])
+            torch.cuda.synchronize()
+            more = ops.kernel_times()
+            for k in ("fwd_ms", "fwd_launches", "bwd_ms", "bwd_launches"):
+                kt[k] += more[k]
         ops.kernel_timing(False)
         return ms_total, kt
+
+
+SAMPLED_STEPS_AFTER = 8  # steps behind the timed region whose every kernel launch is bracketed with events
+
+
+def default_event_stride(steps):
+    """Which launches of the timed region carry events of their own. An event between two kernels undoes their
+    programmatic back-to-back launch for that step (about a quarter of a c2 step), so the sampled share of the region
+    is kept small: about eight launches of a long run, four of a run of a few dozen steps."""
+    return max(1, steps // 8) if steps >= 160 else max(1, -(-steps // 4))
 
 
 def fwd_kernel_name(T, d):
@@ -494,7 +517,7 @@ def extra_workloads(pkg, dev, rank, world, local, peaks, names):
         est = pdist.max_over_ranks(c0.elapsed_time(c1), device=dev) / 3
         steps = int(max(8, min(400, math.ceil(500.0 / max(est, 1e-3)))))
         sampler = ClockSampler(local) if rank == 0 else None
-        ms_total, kt = W.timed_steps(steps, 3, max(1, steps // 8), sampler)
+        ms_total, kt = W.timed_steps(steps, 3, default_event_stride(steps), sampler, after=SAMPLED_STEPS_AFTER)
         clocks = sampler.stop() if sampler else None
         ms = ms_total / steps
         fl = pdist.sum_over_ranks(flops(1, W.BH, T, d), device=dev)
@@ -538,7 +561,8 @@ def main():
     ap.add_argument("--kernel-event-stride", type=int, default=0,
                     help="bracket every N-th launch of each tensor-core kernel with CUDA events inside the timed region "
                          "(roofline durations); events between kernels undo their back-to-back launch, so N=1 slows the "
-                         "step. Default 0 = steps // 8, i.e. about eight sampled launches whatever --steps is")
+                         "step. Default 0 = steps // 8 for 160 steps or more, a quarter of the steps rounded up below; "
+                         "every launch of eight further steps behind the timed region is sampled as well")
     ap.add_argument("--extra", default="c3,c5_512,c5_1024,c5_2048,c5_4096,c5_8192,c5_16384",
                     help="comma-separated other workloads measured briefly (device-timed) after the main one and reported "
                          "under `extra`; empty string: none")
@@ -578,11 +602,11 @@ def main():
     torch.cuda.set_device(dev)
 
     # ---- weak scaling: the global batch is `world` times the per-GPU batch, split by (batch, head) slabs
-    stride = args.kernel_event_stride if args.kernel_event_stride > 0 else max(1, args.steps // 8)
+    stride = args.kernel_event_stride if args.kernel_event_stride > 0 else default_event_stride(args.steps)
     sampler = ClockSampler(local) if rank == 0 else None  # started early: nvidia-smi needs a moment to come up
     W = DeviceWorkload(pkg, dev, rank, world, B, H, T, d)
     BH, n, scale, sets, n_sets, set_bytes, step = W.BH, W.n, W.scale, W.sets, W.n_sets, W.set_bytes, W.step
-    ms_total, kt = W.timed_steps(args.steps, args.warmup, stride, sampler)
+    ms_total, kt = W.timed_steps(args.steps, args.warmup, stride, sampler, after=SAMPLED_STEPS_AFTER)
 
     # ---- the same step replayed from a CUDA graph (the reference's benchmark has such a mode,
     # src/benchmark.cu:158-175): only reported for steps short enough for launch overhead to matter
@@ -741,8 +765,9 @@ def main():
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_tc64_kernel" if d == 64 else "attn_bwd_tc_kernel", "achieved": bwd_tf, "peak": peaks["bf16"],
                      "unit": UNIT, "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} (burst cuBLAS BF16)",
                      "traffic": ncu_traffic_per_launch(args.workload), "launch_ms": bwd_ms,
-                     "timed_launches": kt["bwd_launches"],
-                     "timing": f"CUDA events around every {stride}-th launch inside the timed region (mean)",
+                     "timed_launches": kt["bwd_launches"], "of_which_inside_timed_region": kt["region_bwd_launches"],
+                     "timing": f"CUDA events around every {stride}-th launch inside the timed region and around every launch "
+                               f"of {SAMPLED_STEPS_AFTER} further steps right behind it (mean over all of them)",
                      "flops_per_launch": 5.0 * BH * T * T * d,
                      "forward_kernel": {"kernel": fwd_kernel_name(T, d), "achieved": fwd_tf, "launch_ms": fwd_ms,
                                         "frac": fwd_tf / peaks["bf16"], "timed_launches": kt["fwd_launches"]},
