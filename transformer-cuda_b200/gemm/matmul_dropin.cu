@@ -17,6 +17,7 @@
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 namespace {
 
@@ -326,6 +327,14 @@ struct Twin {
     long long count = 0;
 };
 std::unordered_map<const void*, Twin> g_twins;
+// Twins of a whole buffer that holds many matrices back to back (the optimizer's flat parameter buffer): a matrix that
+// starts inside the buffer at a multiple of 8 elements and has nothing to pad finds its BF16 values at the same offset.
+struct RangeTwin {
+    const float* base = nullptr;
+    long long count = 0;
+    __nv_bfloat16* bf16 = nullptr;
+};
+std::vector<RangeTwin> g_range_twins;
 long long g_twin_hits = 0;
 bool twins_enabled() {
     static const bool v = [] {
@@ -338,7 +347,18 @@ bool twins_enabled() {
 void* find_twin(const void* fp32, int rows, int cols) {
     if (!twins_enabled()) return nullptr;
     auto it = g_twins.find(fp32);
-    if (it == g_twins.end()) return nullptr;
+    if (it == g_twins.end()) {
+        if (rows % 8 || cols % 8) return nullptr;
+        const float* p = static_cast<const float*>(fp32);
+        for (const RangeTwin& r : g_range_twins) {
+            if (p < r.base || p >= r.base + r.count) continue;
+            const long long off = p - r.base;
+            if (off % 8 || off + (long long)rows * cols > r.count) return nullptr;
+            ++g_twin_hits;
+            return r.bf16 + off;
+        }
+        return nullptr;
+    }
     const Twin& t = it->second;
     // a flat twin is the staged layout of any rows x cols view with nothing to pad
     const bool match = t.rows >= 0 ? (t.rows == rows && t.cols == cols)
@@ -482,12 +502,29 @@ extern "C" void* b200gemm_bf16_twin_flat(const void* fp32, long long count) {
     t.rows = -1, t.count = count;
     return t.bf16;
 }
+extern "C" void* b200gemm_bf16_twin_range(const void* fp32, long long count) {
+    if (!fp32 || count <= 0) return nullptr;
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    if (!twins_enabled()) return nullptr;
+    for (const RangeTwin& r : g_range_twins)
+        if (r.base == fp32 && r.count == count) return r.bf16;
+    RangeTwin r;
+    r.base = static_cast<const float*>(fp32), r.count = count;
+    if (cudaMalloc(&r.bf16, size_t(count) * 2) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    g_range_twins.push_back(r);
+    return r.bf16;
+}
 extern "C" long long b200gemm_twin_hits(void) { return g_twin_hits; }
 extern "C" void b200gemm_release_twins(void) {
     std::lock_guard<std::mutex> lock(g_plans_mutex);
     cudaDeviceSynchronize();
     for (auto& kv : g_twins) cudaFree(kv.second.bf16);
     g_twins.clear();
+    for (RangeTwin& r : g_range_twins) cudaFree(r.bf16);
+    g_range_twins.clear();
 }
 extern "C" void b200gemm_forget_staged(void) {
     std::lock_guard<std::mutex> lock(g_plans_mutex);

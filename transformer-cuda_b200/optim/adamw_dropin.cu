@@ -13,14 +13,27 @@
 //   * the update pass moves 16 bytes per thread per stream instead of 4;
 //   * both are deterministic (no floating-point atomics), as the reference's are.
 // The update keeps the reference's expression order (src/optimizer.cu:131-152), so results agree to rounding.
+//
+// When the GEMM drop-in of this repository is in the same link and its BF16 twins are on, the update pass also writes
+// the new parameters as BF16 into a twin of the whole parameter buffer (2 more bytes per parameter), and the GEMMs read
+// the layer weights from there instead of converting each of them twice per step.
 #include "optimizer.h"
+
+#include <cuda_bf16.h>
 
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 
+// Resolved only when the GEMM drop-in is linked in as well (declared in its kernels/matmul.cuh); NULL result: twins off.
+extern "C" void* b200gemm_bf16_twin_range(const void* fp32, long long count) __attribute__((weak));
+
 namespace {
+
+__nv_bfloat16* parameter_twin(const float* params, size_t n) {
+    return b200gemm_bf16_twin_range ? static_cast<__nv_bfloat16*>(b200gemm_bf16_twin_range(params, (long long)n)) : nullptr;
+}
 
 constexpr int kThreads = 256;
 constexpr int kNormCtasPerSm = 8;
@@ -121,7 +134,8 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 template <bool kClip, bool kZero>
 __global__ void __launch_bounds__(kThreads) adamw_kernel(float* __restrict__ params, float* __restrict__ grads,
                                                          float* __restrict__ m, float* __restrict__ v,
-                                                         const float* __restrict__ total_norm, size_t n, AdamArgs a) {
+                                                         const float* __restrict__ total_norm, size_t n, AdamArgs a,
+                                                         __nv_bfloat16* __restrict__ twin) {
     float clip = 1.0f;
     if (kClip) {
         const float norm = *total_norm;
@@ -137,6 +151,12 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(float* __restrict__ par
         adam_one<kClip>(p.z, g.z, mm.z, vv.z, clip, a);
         adam_one<kClip>(p.w, g.w, mm.w, vv.w, clip, a);
         reinterpret_cast<float4*>(params)[i] = p;
+        if (twin) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+            uint2 w;
+            w.x = *reinterpret_cast<const unsigned int*>(&lo), w.y = *reinterpret_cast<const unsigned int*>(&hi);
+            reinterpret_cast<uint2*>(twin)[i] = w;
+        }
         reinterpret_cast<float4*>(m)[i] = mm;
         reinterpret_cast<float4*>(v)[i] = vv;
         if (kZero) reinterpret_cast<float4*>(grads)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -145,6 +165,7 @@ __global__ void __launch_bounds__(kThreads) adamw_kernel(float* __restrict__ par
         float p = params[j], mm = m[j], vv = v[j];
         adam_one<kClip>(p, grads[j], mm, vv, clip, a);
         params[j] = p, m[j] = mm, v[j] = vv;
+        if (twin) twin[j] = __float2bfloat16_rn(p);
         if (kZero) grads[j] = 0.f;
     }
 }
@@ -211,7 +232,8 @@ void AdamW::step(float lr, cudaStream_t stream) {
     step_count++;
     const AdamArgs a{lr, beta1, beta2, eps, weight_decay, 0.f, 1.0f - powf(beta1, (float)step_count),
                      1.0f - powf(beta2, (float)step_count)};
-    adamw_kernel<false, false><<<update_grid(num_params), kThreads, 0, stream>>>(d_params, d_grads, d_m, d_v, nullptr, num_params, a);
+    adamw_kernel<false, false><<<update_grid(num_params), kThreads, 0, stream>>>(d_params, d_grads, d_m, d_v, nullptr, num_params, a,
+                                                                                 parameter_twin(d_params, num_params));
     B200OPT_CHECK(cudaGetLastError());
 }
 
@@ -221,6 +243,7 @@ void AdamW::fused_step(float lr, float max_norm, cudaStream_t stream) {
                      1.0f - powf(beta2, (float)step_count)};
     grad_norm_kernel<<<norm_grid(), kThreads, 0, stream>>>(d_grads, num_params, d_norm_buffer);
     adamw_kernel<true, true><<<update_grid(num_params), kThreads, 0, stream>>>(d_params, d_grads, d_m, d_v,
-                                                                              norm_scratch(d_norm_buffer).total, num_params, a);
+                                                                              norm_scratch(d_norm_buffer).total, num_params, a,
+                                                                              parameter_twin(d_params, num_params));
     B200OPT_CHECK(cudaGetLastError());
 }
