@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <vector>
 
 #include "kernels/matmul.cuh"
@@ -170,6 +171,61 @@ int main(int argc, char** argv) {
         printf("{\"case\": \"backward_pair_dx\", \"max_rel\": %.3e, \"staged_reuses\": %lld, \"ok\": %s}\n", max_rel,
                b200gemm_staged_reuses() - before, ok ? "true" : "false");
         cudaFree(dXa); cudaFree(ddY); cudaFree(dW); cudaFree(ddW); cudaFree(ddX);
+    }
+    // a BF16 twin of a flat buffer that holds matrices back to back (what the AdamW drop-in keeps of the parameters): the
+    // twin is filled with TWICE the FP32 values here, so a product that reads it is told apart from one that converts
+    {
+        const int R = 4096, C1 = 768, C2 = 3072, lead = 128;
+        const size_t nw = size_t(C1) * C2, total = lead + nw + 5;
+        std::vector<float> P(total), X(size_t(R) * C1), Y(size_t(R) * C2);
+        for (auto& x : P) x = next_uniform();
+        for (auto& x : X) x = next_uniform();
+        float *dP, *dXa, *dYa;
+        CK(cudaMalloc(&dP, total * 4)); CK(cudaMalloc(&dXa, X.size() * 4)); CK(cudaMalloc(&dYa, Y.size() * 4));
+        CK(cudaMemcpy(dP, P.data(), total * 4, cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(dXa, X.data(), X.size() * 4, cudaMemcpyHostToDevice));
+        void* twin = b200gemm_bf16_twin_range(dP, (long long)total);
+        if (!twin) {
+            printf("{\"case\": \"range_twin\", \"twins\": \"off\", \"ok\": true}\n");
+        } else {
+            std::vector<unsigned short> T(total);
+            for (size_t i = 0; i < total; ++i) {
+                const float f = 2.0f * P[i];
+                unsigned int u;
+                memcpy(&u, &f, 4);
+                T[i] = (unsigned short)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);  // round to nearest even
+            }
+            CK(cudaMemcpy(twin, T.data(), total * 2, cudaMemcpyHostToDevice));
+            double rel_at[2];
+            for (int which = 0; which < 2; ++which) {
+                // offset 128: read from the twin (factor 2); offset 133: not a multiple of 128, converted as usual (factor 1)
+                const size_t off = which == 0 ? lead : lead + 5;
+                const double factor = which == 0 ? 2.0 : 1.0;
+                b200gemm_forget_staged();
+                matmul_cublaslt(lt, dXa, dP + off, dYa, R, C2, C1, CUBLASLT_EPILOGUE_DEFAULT, nullptr, workspace, ws_bytes, false, false,
+                                1.0f, 0.0f, 0);
+                CK(cudaDeviceSynchronize());
+                CK(cudaMemcpy(Y.data(), dYa, Y.size() * 4, cudaMemcpyDeviceToHost));
+                double max_rel = 0.0;
+                for (int s_ = 0; s_ < 2000; ++s_) {
+                    const int i = int((next_uniform() * 0.5f + 0.5f) * R) % R, j = int((next_uniform() * 0.5f + 0.5f) * C2) % C2;
+                    double acc = 0.0, scale = 0.0;
+                    for (int k = 0; k < C1; ++k) {
+                        const double p = double(X[size_t(i) * C1 + k]) * P[off + size_t(k) * C2 + j];
+                        acc += p, scale += fabs(p);
+                    }
+                    const double rel = fabs(double(Y[size_t(i) * C2 + j]) - factor * acc) / (factor * scale / sqrt(double(C1)) + 1.0);
+                    if (!(rel <= max_rel)) max_rel = rel;
+                }
+                rel_at[which] = max_rel;
+            }
+            const bool ok = rel_at[0] <= tol && rel_at[1] <= tol;
+            all_ok = all_ok && ok;
+            printf("{\"case\": \"range_twin\", \"twins\": \"on\", \"max_rel_from_twin\": %.3e, \"max_rel_converted\": %.3e, \"ok\": %s}\n",
+                   rel_at[0], rel_at[1], ok ? "true" : "false");
+            b200gemm_release_twins();
+        }
+        cudaFree(dP); cudaFree(dXa); cudaFree(dYa);
     }
     const int fault = b200gemm_check_device_fault();
     printf("{\"tcgen05_kernel_launches\": %lld, \"device_fault\": %d}\n", b200gemm_tc_launches(), fault);

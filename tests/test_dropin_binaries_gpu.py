@@ -123,7 +123,7 @@ def test_gemm_wrappers_against_host_fp64(mode, tol, kernel):
                          env=dict(os.environ, B200GEMM_MATH=mode, B200GEMM_KERNEL=kernel))
     assert res.returncode == 0, res.stdout + res.stderr
     assert "b200gemm:" not in res.stderr
-    assert res.stdout.count('"ok": true') == 14 and '"ok": false' not in res.stdout, res.stdout
+    assert res.stdout.count('"ok": true') == 15 and '"ok": false' not in res.stdout, res.stdout
     import json
     tail = json.loads(res.stdout.strip().splitlines()[-1])
     assert tail["device_fault"] == 0
@@ -141,6 +141,20 @@ def test_staged_operand_reuse_between_the_backward_pair():
         assert res.returncode == 0, res.stdout + res.stderr
         pair = [json.loads(l) for l in res.stdout.splitlines() if "backward_pair_dx" in l][0]
         assert pair["ok"] and pair["staged_reuses"] == want, pair
+
+
+def test_weights_inside_a_flat_buffer_are_read_from_its_bf16_twin():
+    """B200GEMM_TWINS=1: a matrix that starts inside a registered flat buffer (b200gemm_bf16_twin_range - what the AdamW
+    drop-in keeps of the parameters) at a multiple of 128 elements is read from the twin - gemm_check fills the twin with
+    twice the FP32 values, so the product doubles - and one at any other offset is converted as usual; without the switch
+    no twin is handed out."""
+    import json
+    for flag, want in (("1", "on"), ("0", "off")):
+        res = subprocess.run([_binary("gemm_check"), "2e-2"], capture_output=True, text=True, timeout=900,
+                             env=dict(os.environ, B200GEMM_MATH="bf16", B200GEMM_TWINS=flag))
+        assert res.returncode == 0, res.stdout + res.stderr
+        line = [json.loads(l) for l in res.stdout.splitlines() if "range_twin" in l][0]
+        assert line["ok"] and line["twins"] == want, line
 
 
 @pytest.mark.parametrize("case", ["parity_audit", "parity_audit_d64"])

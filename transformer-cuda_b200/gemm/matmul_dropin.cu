@@ -328,7 +328,7 @@ struct Twin {
 };
 std::unordered_map<const void*, Twin> g_twins;
 // Twins of a whole buffer that holds many matrices back to back (the optimizer's flat parameter buffer): a matrix that
-// starts inside the buffer at a multiple of 8 elements and has nothing to pad finds its BF16 values at the same offset.
+// starts inside the buffer at a multiple of 128 elements and has nothing to pad finds its BF16 values at the same offset.
 struct RangeTwin {
     const float* base = nullptr;
     long long count = 0;
@@ -353,7 +353,8 @@ void* find_twin(const void* fp32, int rows, int cols) {
         for (const RangeTwin& r : g_range_twins) {
             if (p < r.base || p >= r.base + r.count) continue;
             const long long off = p - r.base;
-            if (off % 8 || off + (long long)rows * cols > r.count) return nullptr;
+            // 256-byte aligned BF16 operands, as the staged copies are: the library's kernels were chosen for that
+            if (off % 128 || off + (long long)rows * cols > r.count) return nullptr;
             ++g_twin_hits;
             return r.bf16 + off;
         }
