@@ -39,3 +39,16 @@ def test_other_ranks_of_the_reference_arm_exit_quietly():
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert res.returncode == 0 and res.stdout.strip() == ""
+
+
+def test_sampled_launches_of_the_timed_region():
+    """Events around a kernel undo its back-to-back launch, so a short timed region carries four sampled steps and a
+    long one about eight; together with the eight steps sampled behind the region every run has at least eight samples."""
+    sys.path.insert(0, ROOT)
+    import bench
+    for steps in (1, 3, 8, 20, 50, 159, 160, 2000):
+        stride = bench.default_event_stride(steps)
+        inside = steps // stride
+        assert stride >= 1 and 1 <= inside <= 8, (steps, stride, inside)
+        assert inside + bench.SAMPLED_STEPS_AFTER >= 8
+    assert bench.default_event_stride(20) == 5 and bench.default_event_stride(2000) == 250
