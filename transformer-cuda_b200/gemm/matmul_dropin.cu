@@ -518,6 +518,16 @@ extern "C" void* b200gemm_bf16_twin_range(const void* fp32, long long count) {
     g_range_twins.push_back(r);
     return r.bf16;
 }
+extern "C" void b200gemm_drop_twin_range(const void* fp32) {
+    std::lock_guard<std::mutex> lock(g_plans_mutex);
+    for (size_t i = 0; i < g_range_twins.size(); ++i) {
+        if (g_range_twins[i].base != fp32) continue;
+        cudaDeviceSynchronize();  // a product that reads the twin may still be running
+        cudaFree(g_range_twins[i].bf16);
+        g_range_twins.erase(g_range_twins.begin() + i);
+        return;
+    }
+}
 extern "C" long long b200gemm_twin_hits(void) { return g_twin_hits; }
 extern "C" void b200gemm_release_twins(void) {
     std::lock_guard<std::mutex> lock(g_plans_mutex);

@@ -28,6 +28,7 @@
 
 // Resolved only when the GEMM drop-in is linked in as well (declared in its kernels/matmul.cuh); NULL result: twins off.
 extern "C" void* b200gemm_bf16_twin_range(const void* fp32, long long count) __attribute__((weak));
+extern "C" void b200gemm_drop_twin_range(const void* fp32) __attribute__((weak));
 
 namespace {
 
@@ -206,6 +207,8 @@ AdamW::AdamW(float* params, float* grads, size_t num_params, const TransformerCo
 }
 
 AdamW::~AdamW() {
+    // the parameters may be freed or rewritten by others once their optimizer is gone: no twin of them may outlive it
+    if (b200gemm_drop_twin_range) b200gemm_drop_twin_range(d_params);
     cudaFree(d_m);
     cudaFree(d_v);
     cudaFree(d_norm_buffer);
