@@ -145,3 +145,11 @@ def test_caller_dropin_headers_keep_reference_signatures():
         out = subprocess.run(["nm", "--defined-only", "-C", os.path.join(libdir, lib)], capture_output=True, text=True, check=True).stdout
         for n in names:
             assert n in out, (lib, n)
+    # every extern "C" extension a drop-in header declares is defined by its library
+    for header, lib in (("matmul.cuh", "libb200gemm.a"), ("layernorm.cuh", "libb200norm.a")):
+        declared = re.findall(r'extern "C" [\w \*]*?\b(b200\w+)\(', text(header))
+        assert declared, header
+        out = subprocess.run(["nm", "--defined-only", os.path.join(libdir, lib)], capture_output=True, text=True, check=True).stdout
+        symbols = {line.split()[-1] for line in out.splitlines() if line.strip()}
+        for name in declared:
+            assert name in symbols, (lib, name)
