@@ -452,6 +452,7 @@ class DeviceWorkload:
         pdist.barrier()
         ms_total = pdist.max_over_ranks(e0.elapsed_time(e1), device=self.dev)
         kt = ops.kernel_times()
+        kt["fwd_samples"], kt["bwd_samples"] = ops.kernel_time_samples(False), ops.kernel_time_samples(True)
         # further steps right after the timed region, same buffers and stream, every launch bracketed: the events that
         # cost the timed region its back-to-back launches cost nothing here, so short runs still get enough samples
         kt["region_bwd_launches"], kt["region_fwd_launches"] = kt["bwd_launches"], kt["fwd_launches"]
@@ -463,6 +464,8 @@ class DeviceWorkload:
             more = ops.kernel_times()
             for k in ("fwd_ms", "fwd_launches", "bwd_ms", "bwd_launches"):
                 kt[k] += more[k]
+            kt["fwd_samples"] += ops.kernel_time_samples(False)
+            kt["bwd_samples"] += ops.kernel_time_samples(True)
         ops.kernel_timing(False)
         return ms_total, kt
 
@@ -516,9 +519,15 @@ def fwd_kernel_name(T, d):
     return "attn_fwd_tc_short_kernel" if (d == 64 or T <= 4096) else "attn_fwd_tc_kernel"
 
 
+def median(xs):
+    xs = sorted(xs)
+    return 0.0 if not xs else (xs[len(xs) // 2] if len(xs) & 1 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2]))
+
+
 def kernel_rooflines(kt, BH, T, d, peaks):
-    bwd_ms = kt["bwd_ms"] / max(1, kt["bwd_launches"])
-    fwd_ms = kt["fwd_ms"] / max(1, kt["fwd_launches"])
+    """Per-launch duration (the median of the sampled launches) and the rate it means, backward and forward kernel."""
+    bwd_ms = median(kt["bwd_samples"])
+    fwd_ms = median(kt["fwd_samples"])
     bwd_tf = 5.0 * BH * T * T * d / (bwd_ms * 1e-3) / 1e12 if bwd_ms > 0 else 0.0
     fwd_tf = 2.0 * BH * T * T * d / (fwd_ms * 1e-3) / 1e12 if fwd_ms > 0 else 0.0
     return bwd_ms, fwd_ms, bwd_tf, fwd_tf
@@ -789,9 +798,10 @@ def main():
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_tc64_kernel" if d == 64 else "attn_bwd_tc_kernel", "achieved": bwd_tf, "peak": peaks["bf16"],
                      "unit": UNIT, "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} (burst cuBLAS BF16)",
                      "traffic": ncu_traffic_per_launch(args.workload), "launch_ms": bwd_ms,
+                     "launch_ms_mean": kt["bwd_ms"] / max(1, kt["bwd_launches"]),
                      "timed_launches": kt["bwd_launches"], "of_which_inside_timed_region": kt["region_bwd_launches"],
                      "timing": f"CUDA events around every {stride}-th launch inside the stream-launched timed region and around every launch "
-                               f"of {SAMPLED_STEPS_AFTER} further steps right behind it (mean over all of them)",
+                               f"of {SAMPLED_STEPS_AFTER} further steps right behind it (median over all of them)",
                      "flops_per_launch": 5.0 * BH * T * T * d,
                      "forward_kernel": {"kernel": fwd_kernel_name(T, d), "achieved": fwd_tf, "launch_ms": fwd_ms,
                                         "frac": fwd_tf / peaks["bf16"], "timed_launches": kt["fwd_launches"]},

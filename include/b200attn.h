@@ -84,6 +84,10 @@ int b200attn_selftest_bounded_wait(unsigned int* report, b200attn_stream_t strea
  * the reference times whole phases with its GpuTimer (include/common.h:35-62). */
 int b200attn_kernel_timing(int enable);
 int b200attn_kernel_times(double* fwd_ms_total, int* fwd_launches, double* bwd_ms_total, int* bwd_launches);
+/* The single durations behind those sums, in launch order: up to `capacity` of the recorded launches of the
+ * forward (backward = 0) or backward (backward = 1) kernel are written to `ms` (a HOST array, may be NULL
+ * with capacity 0) and `count` receives how many were recorded in all. */
+int b200attn_kernel_time_samples(int backward, float* ms, int capacity, int* count);
 
 /* ------------------------------------------------------------------ FP32 API (drop-in) -------- */
 /* (B,T,3*H*d) -> q,k,v (B,H,T,d).  Replaces qkv_split_transpose_forward,

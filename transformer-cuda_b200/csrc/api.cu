@@ -471,6 +471,27 @@ extern "C" int b200attn_kernel_times(double* fwd_ms_total, int* fwd_launches, do
     return B200ATTN_OK;
 }
 
+extern "C" int b200attn_kernel_time_samples(int backward, float* ms_out, int capacity, int* count) {
+    if (capacity < 0 || (capacity > 0 && !ms_out))
+        return fail(B200ATTN_ERR_INVALID_ARGUMENT, "b200attn_kernel_time_samples: capacity %d with %s array", capacity,
+                    ms_out ? "an" : "no");
+    std::lock_guard<std::mutex> lock(g_timed_mutex);
+    const int kind = backward ? 1 : 0;
+    int n = 0;
+    for (auto& t : g_timed) {
+        if (t.kind != kind) continue;
+        if (n < capacity) {
+            RETURN_IF_CUDA(cudaEventSynchronize(t.stop), "cudaEventSynchronize");
+            float ms = 0.f;
+            RETURN_IF_CUDA(cudaEventElapsedTime(&ms, t.start, t.stop), "cudaEventElapsedTime");
+            ms_out[n] = ms;
+        }
+        ++n;
+    }
+    if (count) *count = n;
+    return B200ATTN_OK;
+}
+
 // ====================================================================== FP32 API
 extern "C" int b200attn_qkv_split_f32(const float* qkv, float* q, float* k, float* v, int B, int T, int H, int d,
                                       b200attn_stream_t stream) {

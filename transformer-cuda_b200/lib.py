@@ -39,6 +39,7 @@ _SIGNATURES = {
     "b200attn_kernel_timing": ([_I], _I),
     "b200attn_kernel_times": ([ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_I), ctypes.POINTER(ctypes.c_double),
                                ctypes.POINTER(_I)], _I),
+    "b200attn_kernel_time_samples": ([_I, ctypes.POINTER(ctypes.c_float), _I, ctypes.POINTER(_I)], _I),
     "b200attn_qkv_split_f32": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_qkv_merge_grad_f32": ([_P, _P, _P, _P, _I, _I, _I, _I, _P], _I),
     "b200attn_causal_softmax_fwd_f32": ([_P, _P, _I, _I, _I, _F, _P], _I),

@@ -280,3 +280,15 @@ def kernel_times():
     nf, nb = ctypes.c_int(0), ctypes.c_int(0)
     _lib.call("b200attn_kernel_times", ctypes.byref(f), ctypes.byref(nf), ctypes.byref(b), ctypes.byref(nb))
     return dict(fwd_ms=f.value, fwd_launches=nf.value, bwd_ms=b.value, bwd_launches=nb.value)
+
+
+def kernel_time_samples(backward):
+    """The single launch durations (ms, launch order) of the forward (False) or backward (True) kernel recorded since
+    kernel_timing(True)."""
+    n = ctypes.c_int(0)
+    _lib.call("b200attn_kernel_time_samples", int(bool(backward)), None, 0, ctypes.byref(n))
+    if n.value == 0:
+        return []
+    buf = (ctypes.c_float * n.value)()
+    _lib.call("b200attn_kernel_time_samples", int(bool(backward)), buf, n.value, ctypes.byref(n))
+    return list(buf)
